@@ -1,0 +1,103 @@
+/* omchat_b200 sequence-step kernels: the second C-ABI library (libomchat_b200_seq.so).
+ *
+ * Kernels for decoders that keep their residual stream in fp32 and run packed "steps" (portions of prompts beside single
+ * decoded tokens) against a paged cache: latent (compressed key/value) attention with an optional softmax sink, rotary
+ * tables with pairwise-interleaved layout and optional frequency blending, output-side RMS norms, a score-corrected router
+ * with identity experts, and a linear layer for any shape and for fp32 as well as bf16 storage. Same conventions as
+ * omchat_b200.h: device pointers + sizes, leading dimensions in ELEMENTS, asynchronous on `stream`, nothing is allocated,
+ * 0 or a negative OMC_ERR_* code is returned and omc_last_error() holds the message.
+ *
+ * dtype codes: OMC_DT_F32 = 0 (float), OMC_DT_BF16 = 1 (raw bf16). Accumulation is always fp32.
+ */
+#ifndef OMCHAT_B200_SEQ_H_
+#define OMCHAT_B200_SEQ_H_
+
+#include <stdint.h>
+
+#include "omchat_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OMC_DT_F32 0
+#define OMC_DT_BF16 1
+
+#define OMC_ACT_NONE 0
+#define OMC_ACT_RELU2 1     /* max(z, 0)^2 */
+#define OMC_ACT_GELU_TANH 2 /* 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) */
+
+/* Y[b][M,N] = act(alpha * X[b][M,K] W[b][N,K]^T) for b < batch, any M, N, K >= 1 (edges are bounds-checked).
+ * x_dt / w_dt / y_dt: dtype codes; allowed (x, w): (f32, f32), (f32, bf16), (bf16, bf16). sx / sw / sy: element offsets
+ * between consecutive batch items (heads that are column slices of one row-major buffer: sx = slice width).
+ * tile_group != NULL (batch must be 1): rows come in tiles of 64; tile i multiplies by W + tile_group[i] * group_stride
+ * (elements) and is skipped when tile_group[i] < 0 - the expert-sorted rows of a mixture-of-experts block. The number of
+ * tiles is ceil(M / 64). Every output element accumulates along K in the same order whatever M is, so a row's result does not
+ * depend on what else is in the batch. */
+int omc_linear(const void* X, int x_dt, long long ldx, long long sx, const void* W, int w_dt, long long ldw, long long sw,
+               void* Y, int y_dt, long long ldy, long long sy, int M, int N, int K, int batch, float alpha, int act,
+               const int32_t* tile_group, long long group_stride, void* stream);
+
+/* h32[t,:] = table[ids[t],:] * scale (fp32 residual stream), xb[t,:] = the same rounded to xb_dt (the first sublayer's
+ * input; NULL to skip). ids int32; ids outside [0, vocab) give zero rows. */
+int omc_embed_scale(const int32_t* ids, int T, const void* table, int t_dt, int C, int vocab, float scale, float* h32,
+                    long long ldh, void* xb, int xb_dt, long long ldxb, void* stream);
+
+/* y[t,:] = x[t,:n] / sqrt(mean(x[t,:n]^2) + eps) * (w or 1 + w). x fp32, w of dtype w_dt (NULL: no weight), y of y_dt. */
+int omc_rms_rows(const float* x, long long ldx, const void* w, int w_dt, int one_plus, float eps, void* y, int y_dt,
+                 long long ldy, int rows, int n, void* stream);
+
+/* Output-side norm + residual: h32[t,:] += y[t,:] / sqrt(mean(y[t,:]^2) + eps) * (1 + w); xb[t,:] = round(h32[t,:]) (NULL to skip).
+ * y fp32 (the sublayer's output), w of w_dt. */
+int omc_norm_residual(const float* y, long long ldy, const void* w, int w_dt, float eps, float* h32, long long ldh, void* xb,
+                      int xb_dt, long long ldxb, int rows, int C, void* stream);
+
+/* Latent key/value rows of a step -> paged cache. dkv fp32 [T, r + dr]: the first r columns are RMS-normed with weight w
+ * (plain weight) and stored as the latent; of the last dr columns the first `rot_dims` are rotated pairwise (2i, 2i+1) by
+ * cs[pos[t]] ([n_pos][rot_dims/2][2] fp32: cos, sin of position x pair frequency, built by the host) and all dr are stored behind the latent. Row t goes to page
+ * block_table[slot[t]][pos[t] / page_size], place pos[t] % page_size; the pool is [pages][page_size][r + dr] of pool_dt. */
+int omc_latent_kv_store(const float* dkv, long long ld, int T, int r, int dr, const void* w, int w_dt, float eps, const float* cs,
+                        int rot_dims, const int32_t* pos, const int32_t* slot, const int32_t* block_table, int max_pages,
+                        int page_size, void* pool, int pool_dt, void* stream);
+
+/* Rotated query parts: q32 fp32 [T, H * (dn + dr)] (per head dn unrotated then dr rotated dims) -> qcat[t][h][r + j] for
+ * j < dr (qcat is [T, H, r + dr] of q_dt; its first r columns per head are written by the absorbing omc_linear). */
+int omc_rotary_q(const float* q32, long long ldq, int T, int H, int dn, int dr, const float* cs, int rot_dims,
+                 const int32_t* pos, void* qcat, int q_dt, int r, void* stream);
+
+/* Paged latent attention, any sizes (the plain kernel: fp32 arithmetic, one CTA per (row, head)).
+ * qcat [T, H, r + dr] (absorbed query | rotated query), pool as omc_latent_kv_store writes it. Row t of slot[t] at position
+ * pos[t] sees the cached entries 0..pos[t] of its slot: score_j = qcat[t,h] . entry_j * scale, softmax over j with the optional
+ * extra denominator term exp(sink[h]) (sink fp32 [H] or NULL), out[t,h,:] = sum_j p_j entry_j[:r] (fp32 [T, H, r]). r <= 1024. */
+int omc_latent_attn(const void* qcat, int q_dt, int T, int H, int r, int dr, const void* pool, int pool_dt,
+                    const int32_t* block_table, int max_pages, int page_size, const int32_t* pos, const int32_t* slot,
+                    const float* sink, float scale, float* out, void* stream);
+
+/* Router with score correction and identity experts. z fp32 [T, ldz]: logits of E_tot = experts + identity outputs, and, when
+ * has_gate, one more column: the shared expert's gate logit. s = softmax(z[:E_tot]); choice = s + correction (fp32 [E_tot] or
+ * NULL); the `top` largest choices (ties: lowest index) -> ids int32 [T, top], weights = s of the chosen, not renormalised
+ * -> w fp32 [T, top]; gate[t] = sigmoid(z[t, E_tot]); counts[e] += 1 for every chosen e < experts (identity experts - the
+ * last E_tot - experts outputs - take no rows). E_tot <= 4096, top <= 32. */
+int omc_router_topk(const float* z, long long ldz, int T, int E_tot, int experts, int top, const float* correction, int has_gate,
+                    int32_t* ids, float* w, float* gate, int32_t* counts, void* stream);
+
+/* Expert-sorted layout. plan: seg_start[e] = first row of expert e's segment, segments padded to whole `tile`-row tiles;
+ * tile_group[i] = expert of tile i or -1 (max_tiles entries are written); counts and cursor are left zeroed for the next call.
+ * scatter: row t is copied to one row of the segment of each chosen expert; slot_of[t, j] = that row, or -1 for an identity
+ * expert. xs rows [max_tiles * tile, C] of dtype dt. */
+int omc_moe_plan_tiles(int32_t* counts, int experts, int tile, int max_tiles, int32_t* seg_start, int32_t* cursor,
+                       int32_t* tile_group, void* stream);
+int omc_moe_scatter_rows(const void* x, int dt, long long ldx, int T, int C, const int32_t* ids, int top, int experts,
+                         const int32_t* seg_start, int32_t* cursor, int32_t* slot_of, void* xs, long long ldxs, void* stream);
+
+/* Combine + output-side norm + residual in one pass over the row:
+ * y = sum_j w[t,j] * (slot_of[t,j] >= 0 ? ys[slot_of[t,j]] : h32[t]) + gate[t] * ysh[t]   (ysh / gate may be NULL)
+ * h32[t] += y / sqrt(mean(y^2) + eps) * (1 + nw);  xb[t] = round(h32[t]) (NULL to skip). ys / ysh fp32. */
+int omc_moe_combine_norm(const float* ys, long long ldys, const int32_t* slot_of, const float* w, int top, const float* gate,
+                         const float* ysh, long long ldysh, const void* nw, int nw_dt, float eps, float* h32, long long ldh,
+                         void* xb, int xb_dt, long long ldxb, int T, int C, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OMCHAT_B200_SEQ_H_ */

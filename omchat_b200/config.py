@@ -135,3 +135,145 @@ class OmChatQwen2MoeConfig(OmChatQwen2Config):
     def layer_is_sparse(self, li: int) -> bool:
         """Qwen2MoeDecoderLayer.__init__ (transformers modeling_qwen2_moe.py:381-386)."""
         return li not in self.mlp_only_layers and self.num_experts > 0 and (li + 1) % self.decoder_sparse_step == 0
+
+
+# ---------------------------------------------------------------------------------------------------------------------------
+# Voduzen: a decoder-only language model described by a per-layer list (config.json: architecture "Voduzen").
+
+
+@dataclass
+class RotarySpec:
+    """Pairwise-interleaved rotary embedding on the first `dims` dimensions of a vector: pair i = (2i, 2i + 1) turns by
+    position * f_i, f_i = base^(-2i/dims). `scaling` (factor, original, fast, slow) blends f_i towards f_i / factor over a
+    linear ramp in i and multiplies cos and sin by 0.1 ln(factor) + 1 (the constants 0.1 and 0.001 are fixed by the design)."""
+    dims: int
+    base: float
+    scaling: Optional[dict] = None
+
+    def frequencies(self):
+        """(f [dims / 2] as Python floats, multiplier of cos / sin) in double precision."""
+        import math
+        half = self.dims // 2
+        f = [self.base ** (-2.0 * i / self.dims) for i in range(half)]
+        mult = 1.0
+        sc = self.scaling
+        if sc:
+            factor, orig = float(sc["factor"]), float(sc["original"])
+
+            def turn_dim(turns: float) -> float:
+                return self.dims * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+            lo = max(math.floor(turn_dim(float(sc["fast"]))), 0)
+            hi = min(math.ceil(turn_dim(float(sc["slow"]))), self.dims - 1)
+            span = max(hi - lo, 0.001)
+            for i in range(half):
+                ramp = min(max((i - lo) / span, 0.0), 1.0)
+                f[i] = f[i] / factor * ramp + f[i] * (1.0 - ramp)
+            mult = 0.1 * math.log(factor) + 1.0
+        return f, mult
+
+
+@dataclass
+class LatentAttentionSpec:
+    """Attention whose keys and values are up-projections of a cached latent of width kv_rank plus one rotated key part of
+    width rot_dim shared by the heads. q_rank: queries go through a normed latent of that width (None: one projection).
+    sink: the softmax denominator has one more learned term per head."""
+    heads: int
+    dim: int        # unrotated query / key dimensions per head
+    rot_dim: int    # rotated query / key dimensions per head
+    vdim: int
+    kv_rank: int
+    scale: float
+    rot: RotarySpec = None
+    q_rank: Optional[int] = None
+    sink: bool = False
+
+
+@dataclass
+class RouterMoeSpec:
+    """Mixture of experts: `experts` feed-forward experts (relu^2, no biases) of width expert_ff followed by `identity`
+    identity outputs of the router; every token uses `top` of them; shared_ff: width of the always-on expert (None: none)."""
+    experts: int
+    identity: int
+    top: int
+    expert_ff: int
+    shared_ff: Optional[int] = None
+
+
+@dataclass
+class VoduzenLayerSpec:
+    type: str
+    mixer: LatentAttentionSpec
+    mlp: Optional[RouterMoeSpec]
+
+
+@dataclass
+class VoduzenConfig:
+    model_type: str = "voduzen"
+    vocab_size: int = 0
+    hidden_size: int = 0
+    embedding_scale: float = 1.0
+    logit_scale: float = 1.0
+    norm_eps: float = 1e-6
+    layers: List[VoduzenLayerSpec] = field(default_factory=list)
+    kv_page_size: int = 64       # engine knob: tokens per cache page
+    eos_token_id: int = -1
+    pad_token_id: int = 0
+
+    MIXERS = ("latent_attention", "latent_attention_2")
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "VoduzenConfig":
+        layers = []
+        for i, ld in enumerate(d["layers"]):
+            typ = ld["type"]
+            if typ not in cls.MIXERS:
+                raise ValueError(f"layer {i}: unknown mixer type {typ!r}")
+            m = ld["mixer"]
+            rot = m.get("rot") or {}
+            rspec = RotarySpec(dims=int(rot.get("dims", m.get("rot_dim", 0))), base=float(rot.get("base", 10000.0)),
+                               scaling=dict(rot["scaling"]) if rot.get("scaling") else None)
+            if rspec.dims > int(m["rot_dim"]) or rspec.dims % 2:
+                raise ValueError(f"layer {i}: rot.dims must be even and at most rot_dim")
+            # the first kind projects queries directly and has a sink; the second sends queries through a latent, plain softmax
+            mix = LatentAttentionSpec(heads=int(m["heads"]), dim=int(m["dim"]), rot_dim=int(m["rot_dim"]), vdim=int(m["vdim"]),
+                                      kv_rank=int(m["kv_rank"]), scale=float(m["scale"]), rot=rspec,
+                                      q_rank=int(m["q_rank"]) if typ == "latent_attention_2" else None,
+                                      sink=typ == "latent_attention")
+            mlp = None
+            md = ld.get("mlp")
+            if md:
+                if md.get("kind", "moe") != "moe":
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {md.get('kind')!r}")
+                r = md["router"]
+                sh = md.get("shared")
+                mlp = RouterMoeSpec(experts=int(r["experts"]), identity=int(r.get("identity", 0)), top=int(r["top"]),
+                                    expert_ff=int(md["expert"]["ff"]), shared_ff=int(sh["ff"]) if sh else None)
+            layers.append(VoduzenLayerSpec(type=typ, mixer=mix, mlp=mlp))
+        return cls(vocab_size=int(d["vocab"]), hidden_size=int(d["width"]),
+                   embedding_scale=float((d.get("embedding") or {}).get("scale", 1.0)),
+                   logit_scale=float(d.get("logit_scale", 1.0)), norm_eps=float((d.get("norm") or {}).get("eps", 1e-6)),
+                   layers=layers, kv_page_size=int(d.get("kv_page_size", 64)), eos_token_id=int(d.get("eos_token_id", -1)),
+                   pad_token_id=int(d.get("pad_token_id", 0)))
+
+    def to_dict(self) -> dict:
+        """The config.json form (round-trips through from_dict)."""
+        out_layers = []
+        for l in self.layers:
+            m = l.mixer
+            rot = {"base": m.rot.base, "dims": m.rot.dims}
+            if m.rot.scaling:
+                rot["scaling"] = dict(m.rot.scaling)
+            md = {"dim": m.dim, "heads": m.heads, "kv_rank": m.kv_rank, "rot": rot, "rot_dim": m.rot_dim, "scale": m.scale,
+                  "vdim": m.vdim}
+            if m.q_rank is not None:
+                md["q_rank"] = m.q_rank
+            mlp = None
+            if l.mlp is not None:
+                mlp = {"kind": "moe", "expert": {"ff": l.mlp.expert_ff},
+                       "router": {"experts": l.mlp.experts, "identity": l.mlp.identity, "top": l.mlp.top},
+                       "shared": {"ff": l.mlp.shared_ff} if l.mlp.shared_ff else None}
+            out_layers.append({"type": l.type, "mixer": md, "mlp": mlp})
+        return {"architecture": "Voduzen", "vocab": self.vocab_size, "width": self.hidden_size,
+                "embedding": {"scale": self.embedding_scale}, "logit_scale": self.logit_scale, "norm": {"eps": self.norm_eps},
+                "layers": out_layers, "kv_page_size": self.kv_page_size, "eos_token_id": self.eos_token_id,
+                "pad_token_id": self.pad_token_id}

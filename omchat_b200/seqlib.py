@@ -1,0 +1,194 @@
+"""ctypes binding of libomchat_b200_seq.so (include/omchat_b200_seq.h): the sequence-step kernels, with torch-tensor wrappers.
+
+Like `lib`, there is no fallback: CPU tensors are refused and a failing call raises. The library is built on first use when a
+fresh checkout has none yet (`build.ensure("seq")`, a few seconds of nvcc).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import lib as _core
+from .lib import OmcError, _need_cuda, _ptr, _stream
+
+_P, _I, _L, _F = c_void_p, c_int, c_longlong, c_float
+DT_F32, DT_BF16 = 0, 1
+ACT_NONE, ACT_RELU2, ACT_GELU_TANH = 0, 1, 2
+LINEAR_TILE = 64  # rows per tile of omc_linear's tile -> group table
+
+SIGNATURES = {
+    "omc_last_error": (c_char_p, []),
+    "omc_linear": (_I, [_P, _I, _L, _L, _P, _I, _L, _L, _P, _I, _L, _L, _I, _I, _I, _I, _F, _I, _P, _L, _P]),
+    "omc_embed_scale": (_I, [_P, _I, _P, _I, _I, _I, _F, _P, _L, _P, _I, _L, _P]),
+    "omc_rms_rows": (_I, [_P, _L, _P, _I, _I, _F, _P, _I, _L, _I, _I, _P]),
+    "omc_norm_residual": (_I, [_P, _L, _P, _I, _F, _P, _L, _P, _I, _L, _I, _I, _P]),
+    "omc_latent_kv_store": (_I, [_P, _L, _I, _I, _I, _P, _I, _F, _P, _I, _P, _P, _P, _I, _I, _P, _I, _P]),
+    "omc_rotary_q": (_I, [_P, _L, _I, _I, _I, _I, _P, _I, _P, _P, _I, _I, _P]),
+    "omc_latent_attn": (_I, [_P, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P, _P, _P, _F, _P, _P]),
+    "omc_router_topk": (_I, [_P, _L, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P]),
+    "omc_moe_plan_tiles": (_I, [_P, _I, _I, _I, _P, _P, _P, _P]),
+    "omc_moe_scatter_rows": (_I, [_P, _I, _L, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P]),
+    "omc_moe_combine_norm": (_I, [_P, _L, _P, _P, _I, _P, _P, _L, _P, _I, _F, _P, _L, _P, _I, _L, _I, _I, _P]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = os.environ.get("OMCHAT_B200_SEQ_LIB")
+    if path is None:
+        from . import build
+        path = str(build.ensure("seq"))
+    if not os.path.exists(path):
+        raise OmcError(f"{path} not found (there is no CPU fallback)")
+    lib = ctypes.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def _check(rc: int, what: str):
+    _core.add_launches(1)
+    if rc != 0:
+        raise OmcError(f"{what} failed ({rc}): {load().omc_last_error().decode(errors='replace')}")
+
+
+def dt_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return DT_F32
+    if dtype == torch.bfloat16:
+        return DT_BF16
+    raise OmcError(f"the sequence-step kernels store float32 or bfloat16, not {dtype}")
+
+
+def _dt(t: Optional[torch.Tensor]) -> int:
+    return DT_F32 if t is None else dt_code(t.dtype)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, M: Optional[int] = None, N: Optional[int] = None,
+           K: Optional[int] = None, ldx: Optional[int] = None, ldw: Optional[int] = None, ldy: Optional[int] = None,
+           batch: int = 1, sx: int = 0, sw: int = 0, sy: int = 0, alpha: float = 1.0, act: int = ACT_NONE,
+           tile_group: Optional[torch.Tensor] = None, group_stride: int = 0) -> torch.Tensor:
+    """out = act(alpha * x @ w^T). With the defaults x [M, K], w [N, K], out [M, N] are 2-D row-strided tensors; the keyword
+    overrides describe batched column slices (heads) or a grouped product over expert-sorted row tiles (see the header)."""
+    _need_cuda(x, w, out, tile_group)
+    M = x.shape[0] if M is None else M
+    K = x.shape[-1] if K is None else K
+    N = w.shape[-2] if N is None else N
+    ldx = x.stride(0) if ldx is None else ldx
+    ldw = w.stride(-2) if ldw is None else ldw
+    ldy = out.stride(0) if ldy is None else ldy
+    rc = load().omc_linear(_ptr(x), _dt(x), ldx, sx, _ptr(w), _dt(w), ldw, sw, _ptr(out), _dt(out), ldy, sy, M, N, K, batch,
+                           alpha, act, _ptr(tile_group), group_stride, _stream())
+    _check(rc, "omc_linear")
+    return out
+
+
+def embed_scale(ids: torch.Tensor, table: torch.Tensor, scale: float, h32: torch.Tensor, xb: Optional[torch.Tensor]):
+    _need_cuda(ids, table, h32, xb)
+    assert ids.dtype == torch.int32 and h32.dtype == torch.float32 and table.is_contiguous()
+    T, C = ids.numel(), table.shape[1]
+    rc = load().omc_embed_scale(_ptr(ids), T, _ptr(table), _dt(table), C, table.shape[0], scale, _ptr(h32), h32.stride(0),
+                                _ptr(xb), _dt(xb), xb.stride(0) if xb is not None else 0, _stream())
+    _check(rc, "omc_embed_scale")
+
+
+def rms_rows(x: torch.Tensor, w: Optional[torch.Tensor], eps: float, out: torch.Tensor, one_plus: bool = False, n: Optional[int] = None):
+    """out[t] = x[t, :n] / rms * (w | 1 + w); x fp32 [rows, >= n]."""
+    _need_cuda(x, w, out)
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and out.stride(1) == 1
+    n = x.shape[1] if n is None else n
+    rc = load().omc_rms_rows(_ptr(x), x.stride(0), _ptr(w), _dt(w), 1 if one_plus else 0, eps, _ptr(out), _dt(out), out.stride(0),
+                             x.shape[0], n, _stream())
+    _check(rc, "omc_rms_rows")
+    return out
+
+
+def norm_residual(y: torch.Tensor, w: torch.Tensor, eps: float, h32: torch.Tensor, xb: Optional[torch.Tensor]):
+    """h32 += y / rms(y) * (1 + w); xb = round(h32)."""
+    _need_cuda(y, w, h32, xb)
+    assert y.dtype == torch.float32 and h32.dtype == torch.float32
+    rc = load().omc_norm_residual(_ptr(y), y.stride(0), _ptr(w), _dt(w), eps, _ptr(h32), h32.stride(0), _ptr(xb), _dt(xb),
+                                  xb.stride(0) if xb is not None else 0, y.shape[0], y.shape[1], _stream())
+    _check(rc, "omc_norm_residual")
+
+
+def latent_kv_store(dkv: torch.Tensor, r: int, dr: int, w: torch.Tensor, eps: float, cs: torch.Tensor, rot_dims: int,
+                    pos: torch.Tensor, slot: torch.Tensor, block_table: torch.Tensor, page_size: int, pool: torch.Tensor):
+    _need_cuda(dkv, w, cs, pos, slot, block_table, pool)
+    assert dkv.dtype == torch.float32 and cs.dtype == torch.float32 and pos.dtype == torch.int32 and slot.dtype == torch.int32
+    assert block_table.dtype == torch.int32 and block_table.is_contiguous() and pool.is_contiguous() and pool.shape[-1] == r + dr
+    rc = load().omc_latent_kv_store(_ptr(dkv), dkv.stride(0), dkv.shape[0], r, dr, _ptr(w), _dt(w), eps, _ptr(cs), rot_dims,
+                                    _ptr(pos), _ptr(slot), _ptr(block_table), block_table.shape[1], page_size, _ptr(pool),
+                                    _dt(pool), _stream())
+    _check(rc, "omc_latent_kv_store")
+
+
+def rotary_q(q32: torch.Tensor, H: int, dn: int, dr: int, cs: torch.Tensor, rot_dims: int, pos: torch.Tensor, qcat: torch.Tensor,
+             r: int):
+    _need_cuda(q32, cs, pos, qcat)
+    assert q32.dtype == torch.float32 and qcat.is_contiguous() and qcat.shape[-1] == r + dr
+    rc = load().omc_rotary_q(_ptr(q32), q32.stride(0), q32.shape[0], H, dn, dr, _ptr(cs), rot_dims, _ptr(pos), _ptr(qcat),
+                             _dt(qcat), r, _stream())
+    _check(rc, "omc_rotary_q")
+
+
+def latent_attn(qcat: torch.Tensor, r: int, dr: int, pool: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                pos: torch.Tensor, slot: torch.Tensor, sink: Optional[torch.Tensor], scale: float, out: torch.Tensor):
+    """qcat [T, H, r + dr] -> out fp32 [T, H, r] (weighted sums of cached latents)."""
+    _need_cuda(qcat, pool, block_table, pos, slot, sink, out)
+    T, H = qcat.shape[0], qcat.shape[1]
+    assert out.dtype == torch.float32 and out.is_contiguous() and qcat.is_contiguous()
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == H)
+    rc = load().omc_latent_attn(_ptr(qcat), _dt(qcat), T, H, r, dr, _ptr(pool), _dt(pool), _ptr(block_table), block_table.shape[1],
+                                page_size, _ptr(pos), _ptr(slot), _ptr(sink), scale, _ptr(out), _stream())
+    _check(rc, "omc_latent_attn")
+    return out
+
+
+def router_topk(z: torch.Tensor, e_tot: int, experts: int, top: int, correction: Optional[torch.Tensor], has_gate: bool,
+                ids: torch.Tensor, w: torch.Tensor, gate: Optional[torch.Tensor], counts: torch.Tensor):
+    _need_cuda(z, correction, ids, w, gate, counts)
+    assert z.dtype == torch.float32 and ids.dtype == torch.int32 and w.dtype == torch.float32 and counts.dtype == torch.int32
+    assert correction is None or correction.dtype == torch.float32
+    rc = load().omc_router_topk(_ptr(z), z.stride(0), z.shape[0], e_tot, experts, top, _ptr(correction), 1 if has_gate else 0,
+                                _ptr(ids), _ptr(w), _ptr(gate), _ptr(counts), _stream())
+    _check(rc, "omc_router_topk")
+
+
+def moe_max_tiles(T: int, top: int, experts: int, tile: int = LINEAR_TILE) -> int:
+    """Upper bound of the row tiles of the expert-sorted layout: every (row, choice) pair plus one partly filled tile per expert."""
+    return (T * top + tile - 1) // tile + experts
+
+
+def moe_plan_tiles(counts, experts: int, tile: int, max_tiles: int, seg_start, cursor, tile_group):
+    _need_cuda(counts, seg_start, cursor, tile_group)
+    rc = load().omc_moe_plan_tiles(_ptr(counts), experts, tile, max_tiles, _ptr(seg_start), _ptr(cursor), _ptr(tile_group), _stream())
+    _check(rc, "omc_moe_plan_tiles")
+
+
+def moe_scatter_rows(x, ids, top: int, experts: int, seg_start, cursor, slot_of, xs):
+    _need_cuda(x, ids, seg_start, cursor, slot_of, xs)
+    assert x.dtype == xs.dtype
+    rc = load().omc_moe_scatter_rows(_ptr(x), _dt(x), x.stride(0), x.shape[0], x.shape[1], _ptr(ids), top, experts, _ptr(seg_start),
+                                     _ptr(cursor), _ptr(slot_of), _ptr(xs), xs.stride(0), _stream())
+    _check(rc, "omc_moe_scatter_rows")
+
+
+def moe_combine_norm(ys: Optional[torch.Tensor], slot_of, w, top: int, gate, ysh: Optional[torch.Tensor], nw, eps: float, h32, xb):
+    _need_cuda(ys, slot_of, w, gate, ysh, nw, h32, xb)
+    rc = load().omc_moe_combine_norm(_ptr(ys), ys.stride(0) if ys is not None else 0, _ptr(slot_of), _ptr(w), top, _ptr(gate),
+                                     _ptr(ysh), ysh.stride(0) if ysh is not None else 0, _ptr(nw), _dt(nw), eps, _ptr(h32),
+                                     h32.stride(0), _ptr(xb), _dt(xb), xb.stride(0) if xb is not None else 0, h32.shape[0],
+                                     h32.shape[1], _stream())
+    _check(rc, "omc_moe_combine_norm")
