@@ -73,6 +73,19 @@ int omc_latent_attn(const void* qcat, int q_dt, int T, int H, int r, int dr, con
                     const int32_t* block_table, int max_pages, int page_size, const int32_t* pos, const int32_t* slot,
                     const float* sink, float scale, float* out, void* stream);
 
+/* Tensor-core version of the same (bf16 only; r a multiple of 16 up to 512, dr a multiple of 16, H <= 64): mma.sync over 64-key
+ * tiles that serve as keys AND values; the 64 rows of a tile are (token, head) pairs. The host lists the work:
+ *   items[i]  = int32[8] (first_row, n_tok, slot, first_pos, key_begin, key_end, part_slot, 0): n_tok <= 64 / H consecutive rows
+ *               of one request at positions first_pos.. against the cached keys [key_begin, key_end) (clipped causally per row).
+ *               part_slot < 0: the item sees all its keys and writes `out`; else it writes its (max, sum, unnormalised output)
+ *               partial to ws_o[part_slot][64][r] / ws_ml[part_slot][64][2] (long decode contexts cut into key ranges);
+ *   merges[i] = int32[4] (first_row * H, n_rows, first part_slot, n_parts): partials that belong together.
+ * The sink term is added where the denominator is completed. Same results as omc_latent_attn up to the bf16 rounding of the
+ * probabilities. */
+int omc_latent_attn_mma(const void* qcat, int T, int H, int r, int dr, const void* pool, const int32_t* block_table, int max_pages,
+                        int page_size, const int32_t* items, int n_items, const int32_t* merges, int n_merges, const float* sink,
+                        float scale, float* out, float* ws_o, float* ws_ml, void* stream);
+
 /* Router with score correction and identity experts. z fp32 [T, ldz]: logits of E_tot = experts + identity outputs, and, when
  * has_gate, one more column: the shared expert's gate logit. s = softmax(z[:E_tot]); choice = s + correction (fp32 [E_tot] or
  * NULL); the `top` largest choices (ties: lowest index) -> ids int32 [T, top], weights = s of the chosen, not renormalised

@@ -188,3 +188,290 @@ extern "C" int omc_latent_attn(const void* qcat, int q_dt, int T, int H, int r, 
   }))
   return check_launch("omc_latent_attn");
 }
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Tensor-core kernel (bf16 storage). Rows of a tile are (token, head) pairs of one sequence portion - 64 consecutive rows of
+// qcat viewed as [T * H, r + dr] - so that all heads of a token share the key tile that is staged for them; a 64-key tile
+// [64][r + dr] in shared memory is the B operand of S = Q K^T as it lies (ldmatrix) and, through ldmatrix.trans over its first
+// r columns, the B operand of O += P V: the cache row is read once for both. 4 row groups of 16 rows x VS value splits = 4 * VS
+// warps; with VS = 2 both warps of a row group compute the same scores and each keeps half of the output columns in registers
+// (r = 512 would need 256 accumulator registers per thread otherwise). Long contexts of decode rows are cut into key ranges that
+// different CTAs take; their (max, sum, unnormalised output) partials are merged by latent_attn_merge_kernel, which also adds
+// the sink term to the denominator.
+namespace omc {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+constexpr int kMmaRows = 64, kMmaKeys = 64;
+
+struct LatMmaArgs {
+  const bf16_t* q;
+  const bf16_t* pool;
+  const int32_t* bt;
+  const int32_t* items;  // [n][8]: first_row, n_tok, slot, first_pos, key_begin, key_end, part_slot (-1: final), unused
+  const float* sink;
+  float* out;
+  float* ws_o;   // [part_slot][64][r]
+  float* ws_ml;  // [part_slot][64][2]
+  int max_pages, page_size, H, r, dr;
+  float scale_log2;
+};
+
+template <int VS, int NV>  // NV: 8-column output tiles per warp; covers r <= VS * NV * 8
+__global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int D = a.r + a.dr, pitch = D + 8;
+  bf16_t* Qs = reinterpret_cast<bf16_t*>(smem_raw);
+  bf16_t* Ks = Qs + kMmaRows * pitch;
+  const int32_t* it = a.items + blockIdx.x * 8;
+  const int first_row = it[0], n_tok = it[1], slot = it[2], first_pos = it[3], kb = it[4], ke = it[5], part = it[6];
+  const int n_rows = n_tok * a.H;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rg = warp & 3, vs = warp >> 2;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int chunks = D >> 3;  // 16-byte pieces per row
+  // stage Q (rows past the portion are zero)
+  {
+    const bf16_t* qsrc = a.q + (long long)first_row * a.H * D;
+    for (int i = tid; i < kMmaRows * chunks; i += blockDim.x) {
+      const int row = i / chunks, c = i - row * chunks;
+      bf16_t* dst = Qs + row * pitch + c * 8;
+      if (row < n_rows) cp_async16(smem_u32(dst), qsrc + (long long)row * D + c * 8);
+      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  const int row0 = rg * 16 + g, row1 = row0 + 8;
+  // last key (inclusive) each of this thread's two rows may see
+  const int lim0 = row0 < n_rows ? first_pos + row0 / a.H : -1;
+  const int lim1 = row1 < n_rows ? first_pos + row1 / a.H : -1;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[NV][4];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  const int nv = a.r >> 3;                       // output tiles in total
+  const int nv_per = (nv + VS - 1) / VS;         // this warp's share: tiles [vs * nv_per, min(nv, (vs + 1) * nv_per))
+  const int nv0 = vs * nv_per;
+  const int32_t* bt = a.bt + (long long)slot * a.max_pages;
+  const int k_end = min(ke, first_pos + n_tok);  // exclusive
+  for (int j0 = kb; j0 < k_end; j0 += kMmaKeys) {
+    __syncthreads();  // the previous tile is no longer read
+    for (int i = tid; i < kMmaKeys * chunks; i += blockDim.x) {
+      const int key = i / chunks, c = i - key * chunks;
+      bf16_t* dst = Ks + key * pitch + c * 8;
+      const int j = j0 + key;
+      if (j < k_end) {
+        const bf16_t* src = a.pool + ((long long)bt[j / a.page_size] * a.page_size + j % a.page_size) * D + c * 8;
+        cp_async16(smem_u32(dst), src);
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    // S = Q K^T for this warp's 16 rows x 64 keys
+    float s[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    const uint32_t q_base = smem_u32(Qs + (rg * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * pitch + 8 * (lane >> 4));
+    const uint32_t k_base = smem_u32(Ks + ((lane & 7) + 8 * (lane >> 4)) * pitch + 8 * ((lane >> 3) & 1));
+    for (int kk = 0; kk < D; kk += 16) {
+      uint32_t a0, a1, a2, a3;
+      ldsm_x4(q_base + kk * 2, a0, a1, a2, a3);
+#pragma unroll
+      for (int n2 = 0; n2 < 4; ++n2) {  // key blocks of 16
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(k_base + (n2 * 16 * pitch + kk) * 2, b0, b1, b2, b3);
+        mma_bf16(s[2 * n2], a0, a1, a2, a3, b0, b1);
+        mma_bf16(s[2 * n2 + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    // mask + online softmax (base-2 exponent, scale folded in)
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const int key = j0 + n * 8 + 2 * t4;
+      s[n][0] = key <= lim0 ? s[n][0] * a.scale_log2 : -INFINITY;
+      s[n][1] = key + 1 <= lim0 ? s[n][1] * a.scale_log2 : -INFINITY;
+      s[n][2] = key <= lim1 ? s[n][2] * a.scale_log2 : -INFINITY;
+      s[n][3] = key + 1 <= lim1 ? s[n][3] * a.scale_log2 : -INFINITY;
+      mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+      mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;  // rows that see nothing yet
+    const float c0 = exp2f(m0 - ms0), c1 = exp2f(m1 - ms1);
+    m0 = mn0;
+    m1 = mn1;
+    float rs0 = 0.f, rs1 = 0.f;
+    uint32_t p[8][2];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const float e0 = exp2f(s[n][0] - ms0), e1 = exp2f(s[n][1] - ms0), e2 = exp2f(s[n][2] - ms1), e3 = exp2f(s[n][3] - ms1);
+      p[n][0] = pack2_bf16(e0, e1);
+      p[n][1] = pack2_bf16(e2, e3);
+      // the denominator sums the ROUNDED probabilities, the ones the numerator uses
+      const float2 f0 = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&p[n][0]));
+      const float2 f1 = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&p[n][1]));
+      rs0 += f0.x + f0.y;
+      rs1 += f1.x + f1.y;
+    }
+    l0 = l0 * c0 + rs0;
+    l1 = l1 * c1 + rs1;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      o[j][0] *= c0;
+      o[j][1] *= c0;
+      o[j][2] *= c1;
+      o[j][3] *= c1;
+    }
+    // O += P V over this warp's output tiles (pairs of 8-column tiles per ldmatrix.x4.trans)
+    const uint32_t v_base = smem_u32(Ks + ((lane & 7) + 8 * ((lane >> 3) & 1)) * pitch + 8 * (lane >> 4));
+#pragma unroll
+    for (int kb16 = 0; kb16 < 4; ++kb16) {
+      const uint32_t a0 = p[2 * kb16][0], a1 = p[2 * kb16][1], a2 = p[2 * kb16 + 1][0], a3 = p[2 * kb16 + 1][1];
+#pragma unroll
+      for (int j = 0; j < NV; j += 2) {
+        const int tile = nv0 + j;
+        if (j < nv_per && tile < nv) {
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4_t(v_base + (kb16 * 16 * pitch + tile * 8) * 2, b0, b1, b2, b3);
+          mma_bf16(o[j], a0, a1, a2, a3, b0, b1);
+          if (j + 1 < nv_per && tile + 1 < nv) mma_bf16(o[j + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+    }
+  }
+  // row sums over the quad
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if (part < 0) {
+    float d0 = l0, d1 = l1;
+    if (a.sink != nullptr) {
+      if (row0 < n_rows) d0 += exp2f(a.sink[row0 % a.H] * 1.4426950408889634f - m0);
+      if (row1 < n_rows) d1 += exp2f(a.sink[row1 % a.H] * 1.4426950408889634f - m1);
+    }
+    const float i0 = 1.f / d0, i1 = 1.f / d1;
+    float* out0 = a.out + ((long long)first_row * a.H + row0) * a.r;
+    float* out1 = a.out + ((long long)first_row * a.H + row1) * a.r;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int tile = nv0 + j;
+      if (j < nv_per && tile < nv) {
+        const int col = tile * 8 + 2 * t4;
+        if (row0 < n_rows) *reinterpret_cast<float2*>(out0 + col) = make_float2(o[j][0] * i0, o[j][1] * i0);
+        if (row1 < n_rows) *reinterpret_cast<float2*>(out1 + col) = make_float2(o[j][2] * i1, o[j][3] * i1);
+      }
+    }
+  } else {
+    float* wo = a.ws_o + (long long)part * kMmaRows * a.r;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int tile = nv0 + j;
+      if (j < nv_per && tile < nv) {
+        const int col = tile * 8 + 2 * t4;
+        *reinterpret_cast<float2*>(wo + (long long)row0 * a.r + col) = make_float2(o[j][0], o[j][1]);
+        *reinterpret_cast<float2*>(wo + (long long)row1 * a.r + col) = make_float2(o[j][2], o[j][3]);
+      }
+    }
+    if (vs == 0 && t4 == 0) {
+      float* ml = a.ws_ml + (long long)part * kMmaRows * 2;
+      ml[row0 * 2] = m0;
+      ml[row0 * 2 + 1] = l0;
+      ml[row1 * 2] = m1;
+      ml[row1 * 2 + 1] = l1;
+    }
+  }
+}
+
+// merges[i] = (first q row = first_row * H, n_rows, first part slot, n_parts): one CTA per group, one warp per row.
+__global__ void __launch_bounds__(256) latent_attn_merge_kernel(const int32_t* __restrict__ merges, const float* __restrict__ ws_o,
+                                                                const float* __restrict__ ws_ml, const float* __restrict__ sink, int H,
+                                                                int r, float* __restrict__ out) {
+  const int32_t* mg = merges + blockIdx.x * 4;
+  const int qrow0 = mg[0], n_rows = mg[1], part0 = mg[2], n_parts = mg[3];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row = warp; row < n_rows; row += 8) {
+    float mt = -INFINITY;
+    for (int p = 0; p < n_parts; ++p) mt = fmaxf(mt, ws_ml[((long long)(part0 + p) * kMmaRows + row) * 2]);
+    float den = 0.f;
+    for (int p = 0; p < n_parts; ++p) {
+      const float* ml = ws_ml + ((long long)(part0 + p) * kMmaRows + row) * 2;
+      if (ml[0] != -INFINITY) den += ml[1] * exp2f(ml[0] - mt);
+    }
+    if (sink != nullptr) den += exp2f(sink[(qrow0 + row) % H] * 1.4426950408889634f - mt);
+    const float inv = 1.f / den;
+    for (int c = lane; c < r; c += 32) {
+      float v = 0.f;
+      for (int p = 0; p < n_parts; ++p) {
+        const float mp = ws_ml[((long long)(part0 + p) * kMmaRows + row) * 2];
+        if (mp != -INFINITY) v += ws_o[((long long)(part0 + p) * kMmaRows + row) * r + c] * exp2f(mp - mt);
+      }
+      out[((long long)qrow0 + row) * r + c] = v * inv;
+    }
+  }
+}
+
+template <int VS, int NV>
+static int launch_lat_mma(const LatMmaArgs& a, int n_items, size_t smem, cudaStream_t st) {
+  static bool attr_done[kMaxDevices] = {};
+  const int dev = cur_device();
+  if (!attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(latent_attn_mma_kernel<VS, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return set_error(OMC_ERR_CUDA, cudaGetErrorString(e));
+    attr_done[dev] = true;
+  }
+  latent_attn_mma_kernel<VS, NV><<<n_items, 128 * VS, smem, st>>>(a);
+  return check_launch("omc_latent_attn_mma");
+}
+
+}  // namespace omc
+
+extern "C" int omc_latent_attn_mma(const void* qcat, int T, int H, int r, int dr, const void* pool, const int32_t* block_table,
+                                   int max_pages, int page_size, const int32_t* items, int n_items, const int32_t* merges,
+                                   int n_merges, const float* sink, float scale, float* out, float* ws_o, float* ws_ml, void* stream) {
+  if (qcat == nullptr || pool == nullptr || block_table == nullptr || items == nullptr || out == nullptr || T < 0 || H <= 0 ||
+      page_size <= 0 || max_pages <= 0 || n_items < 0 || n_merges < 0 || (n_merges > 0 && (merges == nullptr || ws_o == nullptr || ws_ml == nullptr)))
+    return set_error(OMC_ERR_ARG, "omc_latent_attn_mma: bad argument");
+  if (r <= 0 || r % 16 != 0 || r > 512 || dr < 0 || dr % 16 != 0 || H > kMmaRows)
+    return set_error(OMC_ERR_SHAPE, "omc_latent_attn_mma: latent width a multiple of 16 up to 512, rotated width a multiple of 16, at most 64 heads");
+  if (n_items == 0) return OMC_OK;
+  const int D = r + dr;
+  const size_t smem = (size_t)(kMmaRows + kMmaKeys) * (D + 8) * sizeof(bf16_t);
+  if (smem > 227 * 1024) return set_error(OMC_ERR_SHAPE, "omc_latent_attn_mma: rows too wide for shared memory");
+  LatMmaArgs a{static_cast<const bf16_t*>(qcat), static_cast<const bf16_t*>(pool), block_table, items, sink, out, ws_o, ws_ml,
+               max_pages, page_size, H, r, dr, scale * 1.4426950408889634f};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc;
+  if (r <= 64) rc = launch_lat_mma<1, 8>(a, n_items, smem, st);
+  else if (r <= 128) rc = launch_lat_mma<1, 16>(a, n_items, smem, st);
+  else if (r <= 256) rc = launch_lat_mma<2, 16>(a, n_items, smem, st);
+  else rc = launch_lat_mma<2, 32>(a, n_items, smem, st);
+  if (rc != OMC_OK || n_merges == 0) return rc;
+  latent_attn_merge_kernel<<<n_merges, 256, 0, st>>>(merges, ws_o, ws_ml, sink, H, r, out);
+  return check_launch("omc_latent_attn_merge");
+}

@@ -274,7 +274,9 @@ class StepScheduler:
         if toks:
             dev = self.model.device
             self.cache.sync()
-            meta = torch.tensor([toks, pos, slot], dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+            meta = torch.tensor([toks, pos, slot], dtype=torch.int32)
+            if torch.device(dev).type == "cuda":
+                meta = meta.pin_memory().to(dev, non_blocking=True)
             wr = torch.tensor(want, dtype=torch.int64).to(dev) if want else None
             logits = self.model.step(meta[0], meta[1], meta[2], self.cache, wr)
             self.steps_run += 1
