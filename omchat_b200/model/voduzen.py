@@ -171,6 +171,7 @@ class VoduzenDecoder:
         self.C = cfg.hidden_size
         self.eps = cfg.norm_eps
         self.tensor_gemm = dtype == torch.bfloat16
+        self.tensor_attention = True    # False: the plain attention kernel for every shape (A/B, tests)
         self._moe_ws = {}
 
     # ---- cache
@@ -204,7 +205,7 @@ class VoduzenDecoder:
         return seqlib.linear(x, w, out, alpha=alpha, act=act)
 
     # ---- sublayers
-    def _mixer(self, li: int, xb: torch.Tensor, pos, slot, cache: PagedLatentCache) -> torch.Tensor:
+    def _mixer(self, li: int, xb: torch.Tensor, pos, slot, cache: PagedLatentCache, plans: Optional[dict] = None) -> torch.Tensor:
         """-> fp32 [T, C], the mixer's output before its norm."""
         spec, mw = self.cfg.layers[li].mixer, self.w.layers[li].mix
         T = xb.shape[0]
@@ -227,7 +228,13 @@ class VoduzenDecoder:
         seqlib.linear(q32, mw.uk_t, qcat, M=T, N=r, K=dn, ldx=q32.stride(0), sx=dn + dr, ldw=dn, sw=r * dn, ldy=H * (r + dr),
                       sy=r + dr, batch=H)
         olat = torch.empty(T, H, r, device=xb.device, dtype=f32)
-        seqlib.latent_attn(qcat, r, dr, pool, cache.block_table, cache.page_size, pos, slot, mw.sink, spec.scale, olat)
+        if plans is not None and self.tensor_attention and seqlib.latent_attn_mma_ok(H, r, dr, self.dtype):
+            plan = plans.get(H)
+            if plan is None:
+                plan = plans[H] = seqlib.LatentAttnPlan(plans["portions"], H, xb.device)
+            seqlib.latent_attn_mma(qcat, r, dr, pool, cache.block_table, cache.page_size, plan, mw.sink, spec.scale, olat)
+        else:
+            seqlib.latent_attn(qcat, r, dr, pool, cache.block_table, cache.page_size, pos, slot, mw.sink, spec.scale, olat)
         # values: attn[t, h*dv:(h+1)*dv] = W_uv,h @ olat[t, h]
         attn = torch.empty(T, H * dv, device=xb.device, dtype=self.dtype)
         seqlib.linear(olat, mw.uv, attn, M=T, N=dv, K=r, ldx=H * r, sx=r, ldw=r, sw=dv * r, ldy=H * dv, sy=dv, batch=H)
@@ -291,18 +298,21 @@ class VoduzenDecoder:
     # ---- the step
     @torch.no_grad()
     def step(self, tokens: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor, cache: PagedLatentCache,
-             want_rows: Optional[torch.Tensor] = None, collect: Optional[list] = None) -> Optional[torch.Tensor]:
+             want_rows: Optional[torch.Tensor] = None, collect: Optional[list] = None,
+             portions: Optional[Sequence] = None) -> Optional[torch.Tensor]:
         """tokens / pos / slot: int32 [T] on the device - row t is token tokens[t] at position pos[t] of the request in cache
         slot slot[t]; rows of one request are consecutive and ascending in position. Appends every row to the cache and returns
         fp32 logits [len(want_rows), vocab] (None when no row is asked for). collect: receives the residual stream after
-        every layer (debugging / tests)."""
+        every layer (debugging / tests). portions: the same batch as the host knows it, [(first_row, n_rows, slot, first_pos)]
+        per request - the tensor-core attention kernel's work list is built from it; without it the plain kernel runs."""
         T = tokens.numel()
         dev = self.device
+        plans = {"portions": list(portions)} if portions is not None else None
         h32 = torch.empty(T, self.C, device=dev, dtype=torch.float32)
         xb = torch.empty(T, self.C, device=dev, dtype=self.dtype)
         seqlib.embed_scale(tokens, self.w.embed, self.cfg.embedding_scale, h32, xb)
         for li, lw in enumerate(self.w.layers):
-            y32 = self._mixer(li, xb, pos, slot, cache)
+            y32 = self._mixer(li, xb, pos, slot, cache, plans)
             seqlib.norm_residual(y32, lw.norm1, self.eps, h32, xb)
             if lw.mlp is not None:
                 self._moe(li, xb, h32, xb)
@@ -352,9 +362,9 @@ class VoduzenForCausalLM:
     def eval(self):
         return self
 
-    def step(self, tokens, pos, slot, cache, want_rows=None, collect=None):
+    def step(self, tokens, pos, slot, cache, want_rows=None, collect=None, portions=None):
         with torch.cuda.device(self.device):
-            return self.decoder.step(tokens, pos, slot, cache, want_rows, collect)
+            return self.decoder.step(tokens, pos, slot, cache, want_rows, collect, portions)
 
     @torch.no_grad()
     def generate(self, input_ids, max_new_tokens: int = 32, eos_token_id: Optional[int] = None, do_sample: bool = False,

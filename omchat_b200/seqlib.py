@@ -29,6 +29,7 @@ SIGNATURES = {
     "omc_latent_kv_store": (_I, [_P, _L, _I, _I, _I, _P, _I, _F, _P, _I, _P, _P, _P, _I, _I, _P, _I, _P]),
     "omc_rotary_q": (_I, [_P, _L, _I, _I, _I, _I, _P, _I, _P, _P, _I, _I, _P]),
     "omc_latent_attn": (_I, [_P, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P, _P, _P, _F, _P, _P]),
+    "omc_latent_attn_mma": (_I, [_P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _P, _I, _P, _F, _P, _P, _P, _P]),
     "omc_router_topk": (_I, [_P, _L, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P]),
     "omc_moe_plan_tiles": (_I, [_P, _I, _I, _I, _P, _P, _P, _P]),
     "omc_moe_scatter_rows": (_I, [_P, _I, _L, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P]),
@@ -153,6 +154,80 @@ def latent_attn(qcat: torch.Tensor, r: int, dr: int, pool: torch.Tensor, block_t
     rc = load().omc_latent_attn(_ptr(qcat), _dt(qcat), T, H, r, dr, _ptr(pool), _dt(pool), _ptr(block_table), block_table.shape[1],
                                 page_size, _ptr(pos), _ptr(slot), _ptr(sink), scale, _ptr(out), _stream())
     _check(rc, "omc_latent_attn")
+    return out
+
+
+MMA_ROWS = 64  # rows ((token, head) pairs) and keys per tile of the tensor-core latent attention
+
+
+def latent_attn_mma_ok(H: int, r: int, dr: int, dtype: torch.dtype) -> bool:
+    """Shapes the tensor-core kernel takes; everything else runs on the plain kernel."""
+    return (dtype == torch.bfloat16 and H <= MMA_ROWS and r % 16 == 0 and 0 < r <= 512 and dr % 16 == 0
+            and 2 * MMA_ROWS * (r + dr + 8) * 2 <= 227 * 1024)
+
+
+class LatentAttnPlan:
+    """Work list of one step for one head count (omc_latent_attn_mma): items, merge groups and the partial-result workspace.
+    portions: host list of (first_row, n_rows, slot, first_pos) - the consecutive rows of each request in the packed batch.
+    Contexts are cut into key ranges (multiples of 64 keys, at least `min_keys` each) while the step has fewer CTAs than
+    `target_ctas`, so that a few decode rows over a long context still fill the device."""
+
+    def __init__(self, portions, H: int, device, target_ctas: int = 296, min_keys: int = 256):
+        import numpy as np
+        tok = max(1, MMA_ROWS // H)
+        base = sum(-(-n // tok) for _, n, _, _ in portions)
+        items, merges, part = [], [], 0
+        for first_row, n, slot, p0 in portions:
+            starts = np.arange(0, n, tok, dtype=np.int64)
+            ntok = np.minimum(tok, n - starts)
+            keys = p0 + starts + ntok                                  # keys the tile's last row sees
+            parts = np.ones_like(starts)
+            if base < target_ctas // 2:
+                parts = np.clip(np.minimum(-(-keys // min_keys), -(-target_ctas // max(base, 1))), 1, None)
+            for i in range(len(starts)):
+                np_i, k = int(parts[i]), int(keys[i])
+                fr, nt = first_row + int(starts[i]), int(ntok[i])
+                if np_i == 1:
+                    items.append((fr, nt, slot, p0 + int(starts[i]), 0, k, -1, 0))
+                    continue
+                span = -(-(-(-k // np_i)) // MMA_ROWS) * MMA_ROWS       # keys per part, a multiple of 64
+                np_i = -(-k // span)
+                merges.append((fr * H, nt * H, part, np_i))
+                for j in range(np_i):
+                    items.append((fr, nt, slot, p0 + int(starts[i]), j * span, min(k, (j + 1) * span), part, 0))
+                    part += 1
+        self.n_items, self.n_merges, self.n_parts = len(items), len(merges), part
+        flat = torch.tensor(items, dtype=torch.int32).view(-1)
+        flat = torch.cat([flat, torch.tensor(merges, dtype=torch.int32).view(-1)]) if merges else flat
+        buf = flat.pin_memory().to(device, non_blocking=True)
+        self.items = buf[:self.n_items * 8]
+        self.merges = buf[self.n_items * 8:] if merges else None
+
+
+_mma_ws = {}
+
+
+def latent_attn_mma(qcat: torch.Tensor, r: int, dr: int, pool: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                    plan: LatentAttnPlan, sink: Optional[torch.Tensor], scale: float, out: torch.Tensor):
+    _need_cuda(qcat, pool, block_table, plan.items, sink, out)
+    T, H = qcat.shape[0], qcat.shape[1]
+    assert qcat.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and out.dtype == torch.float32
+    assert qcat.is_contiguous() and out.is_contiguous() and pool.is_contiguous()
+    ws_o = ws_ml = None
+    if plan.n_parts:
+        key = (str(qcat.device), torch.cuda.current_stream().cuda_stream)
+        need = plan.n_parts * MMA_ROWS * (r + 2)
+        ws = _mma_ws.get(key)
+        if ws is None or ws.numel() < need:
+            ws = torch.empty(need, device=qcat.device, dtype=torch.float32)
+            _mma_ws[key] = ws
+        ws_o, ws_ml = ws[:plan.n_parts * MMA_ROWS * r], ws[plan.n_parts * MMA_ROWS * r:]
+    rc = load().omc_latent_attn_mma(_ptr(qcat), T, H, r, dr, _ptr(pool), _ptr(block_table), block_table.shape[1], page_size,
+                                    _ptr(plan.items), plan.n_items, _ptr(plan.merges), plan.n_merges, _ptr(sink), scale, _ptr(out),
+                                    _ptr(ws_o), _ptr(ws_ml), _stream())
+    _check(rc, "omc_latent_attn_mma")
+    if plan.n_merges:
+        _core.add_launches(1)
     return out
 
 

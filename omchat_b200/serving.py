@@ -257,6 +257,7 @@ class StepScheduler:
         pos: List[int] = []
         slot: List[int] = []
         want: List[int] = []
+        portions = []
         for key, ids, wanted in entries:
             ids = list(ids)
             if not ids:
@@ -264,6 +265,7 @@ class StepScheduler:
             r = self.live.get(key) or self._admit(key)
             self._grow(r, len(ids))
             base = len(toks)
+            portions.append((base, len(ids), r.slot, r.length))
             toks += ids
             pos += range(r.length, r.length + len(ids))
             slot += [r.slot] * len(ids)
@@ -278,7 +280,7 @@ class StepScheduler:
             if torch.device(dev).type == "cuda":
                 meta = meta.pin_memory().to(dev, non_blocking=True)
             wr = torch.tensor(want, dtype=torch.int64).to(dev) if want else None
-            logits = self.model.step(meta[0], meta[1], meta[2], self.cache, wr)
+            logits = self.model.step(meta[0], meta[1], meta[2], self.cache, wr, portions=portions)
             self.steps_run += 1
         for key in end:
             self.release(key)

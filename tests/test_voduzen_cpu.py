@@ -80,7 +80,7 @@ class _Recorder:
         self.decoder = _Recorder._Dec(self)
         self.batches = []
 
-    def step(self, tokens, pos, slot, cache, want_rows=None, collect=None):
+    def step(self, tokens, pos, slot, cache, want_rows=None, collect=None, portions=None):
         self.batches.append((tokens.tolist(), pos.tolist(), slot.tolist(), cache.table_host.clone()))
         if want_rows is None:
             return None
