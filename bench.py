@@ -294,10 +294,20 @@ def main():
     ap.add_argument("--no-c5", action="store_true", help="skip the c5 leg of the main line (N > 1 only)")
     ap.add_argument("--no-variants", action="store_true", help="skip the Qwen2-MoE / InternViT-300M legs (`variants`, N = 1 only)")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--voduzen", action="append", choices=["s", "m"], help="instead of the default workload: the Voduzen decoder "
+                    "at this size (random weights) beside the Qwen2-MoE decoder at equal size - prefill and decode throughput "
+                    "and the new kernels against their rooflines (tools/bench_voduzen.py); one JSON line per size")
     ap.add_argument("--pixel-shuffle", type=float, default=1.0, help="mm_pixel_shuffle_ratio (1.0 = reference behaviour)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.voduzen:
+        import torch
+        from tools.bench_voduzen import measure as measure_voduzen
+        torch.cuda.set_device(0)
+        for size in args.voduzen:
+            print(json.dumps(measure_voduzen(size, steps=max(args.steps, 8))), flush=True)
         return
 
     import torch

@@ -30,6 +30,7 @@ extern "C" {
 #define OMC_EPI_GELU 1   /* Y = gelu_erf(X W^T + bias) */
 #define OMC_EPI_RES 2    /* Y = res + scale * (X W^T + bias)   (scale, bias optional) */
 #define OMC_EPI_SWIGLU 3 /* W rows alternate gate_i, up_i (row 2i, 2i+1): Y[:, i] = silu(gate_i) * up_i, Y is [M, N/2] */
+#define OMC_EPI_RELU2 4  /* Y = max(X W^T + bias, 0)^2 */
 
 const char* omc_last_error(void);
 int omc_version(void);
@@ -421,6 +422,9 @@ int omc_moe_scatter(const void* x, long long ldx, int T, int C, const int32_t* t
                     int32_t* cursor, void* xperm, long long ldp, int32_t* slot_of, void* stream);
 int omc_gemm_bf16_grouped(const void* X, long long ldx, int M_max, const void* W, long long ldw, int n_experts, int N, int K,
                           const int32_t* tile_expert, int active_tiles_hint, void* out, long long ldo, int epi, void* stream);
+/* The same with fp32 output (epi OMC_EPI_NONE or OMC_EPI_RELU2): expert outputs that a combine kernel sums in fp32. */
+int omc_gemm_bf16_grouped_f32(const void* X, long long ldx, int M_max, const void* W, long long ldw, int n_experts, int N, int K,
+                              const int32_t* tile_expert, int active_tiles_hint, float* out, long long ldo, int epi, void* stream);
 int omc_moe_combine(void* h, long long ldh, int T, int C, const void* yperm, long long ldy, const int32_t* slot_of,
                     const float* topk_w, int top_k, const void* shared_y, long long lds, const float* shared_gate, float* ssq_out,
                     int ssq_parts, void* stream);

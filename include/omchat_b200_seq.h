@@ -60,9 +60,9 @@ int omc_latent_kv_store(const float* dkv, long long ld, int T, int r, int dr, co
                         int rot_dims, const int32_t* pos, const int32_t* slot, const int32_t* block_table, int max_pages,
                         int page_size, void* pool, int pool_dt, void* stream);
 
-/* Rotated query parts: q32 fp32 [T, H * (dn + dr)] (per head dn unrotated then dr rotated dims) -> qcat[t][h][r + j] for
+/* Rotated query parts: q [T, H * (dn + dr)] of in_dt (per head dn unrotated then dr rotated dims) -> qcat[t][h][r + j] for
  * j < dr (qcat is [T, H, r + dr] of q_dt; its first r columns per head are written by the absorbing omc_linear). */
-int omc_rotary_q(const float* q32, long long ldq, int T, int H, int dn, int dr, const float* cs, int rot_dims,
+int omc_rotary_q(const void* q, int in_dt, long long ldq, int T, int H, int dn, int dr, const float* cs, int rot_dims,
                  const int32_t* pos, void* qcat, int q_dt, int r, void* stream);
 
 /* Paged latent attention, any sizes (the plain kernel: fp32 arithmetic, one CTA per (row, head)).
@@ -80,11 +80,16 @@ int omc_latent_attn(const void* qcat, int q_dt, int T, int H, int r, int dr, con
  *               part_slot < 0: the item sees all its keys and writes `out`; else it writes its (max, sum, unnormalised output)
  *               partial to ws_o[part_slot][64][r] / ws_ml[part_slot][64][2] (long decode contexts cut into key ranges);
  *   merges[i] = int32[4] (first_row * H, n_rows, first part_slot, n_parts): partials that belong together.
- * The sink term is added where the denominator is completed. Same results as omc_latent_attn up to the bf16 rounding of the
- * probabilities. */
+ * The sink term is added where the denominator is completed. out [T, H, r] of out_dt (fp32 or bf16). Same results as
+ * omc_latent_attn up to the bf16 rounding of the probabilities. */
 int omc_latent_attn_mma(const void* qcat, int T, int H, int r, int dr, const void* pool, const int32_t* block_table, int max_pages,
                         int page_size, const int32_t* items, int n_items, const int32_t* merges, int n_merges, const float* sink,
-                        float scale, float* out, float* ws_o, float* ws_ml, void* stream);
+                        float scale, void* out, int out_dt, float* ws_o, float* ws_ml, void* stream);
+
+/* The work list of a decode-only step, written on the device from pos / slot (one row per request, `parts` <= 64 key ranges each):
+ * items int32 [B * parts][8], merges int32 [B][4] (untouched when parts == 1). Lets a CUDA graph replay the step as contexts grow. */
+int omc_latent_decode_items(const int32_t* pos, const int32_t* slot, int B, int H, int parts, int32_t* items, int32_t* merges,
+                            void* stream);
 
 /* Router with score correction and identity experts. z fp32 [T, ldz]: logits of E_tot = experts + identity outputs, and, when
  * has_gate, one more column: the shared expert's gate logit. s = softmax(z[:E_tot]); choice = s + correction (fp32 [E_tot] or

@@ -196,6 +196,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         continue;
       }
       if (p.epi == EPI_GELU) v = sk_gelu(v);
+      else if (p.epi == EPI_RELU2) v = fmaxf(v, 0.f) * fmaxf(v, 0.f);
       else if (p.epi == EPI_RES && n_ok) v = resv[m] + scale_n * v;
       if (n_ok) {
         if (p.out_f32 != nullptr) p.out_f32[(long long)m * p.ldo + n] = v;
@@ -290,7 +291,7 @@ extern "C" int omc_gemm_skinny_bf16(const void* X, long long ldx, const void* W,
   if (M <= 0 || N <= 0 || K <= 0) return set_error(OMC_ERR_SHAPE, "omc_gemm_skinny_bf16: empty problem");
   if (M > 64) return set_error(OMC_ERR_SHAPE, "omc_gemm_skinny_bf16: M must be <= 64 (use omc_gemm_bf16)");
   if (N % 8 != 0 || K % 8 != 0) return set_error(OMC_ERR_SHAPE, "omc_gemm_skinny_bf16: N and K must be multiples of 8");
-  if (epi < EPI_NONE || epi > EPI_SWIGLU) return set_error(OMC_ERR_ARG, "omc_gemm_skinny_bf16: unknown epilogue");
+  if (epi < EPI_NONE || epi > EPI_RELU2) return set_error(OMC_ERR_ARG, "omc_gemm_skinny_bf16: unknown epilogue");
   if (epi == EPI_RES && res == nullptr) return set_error(OMC_ERR_ARG, "omc_gemm_skinny_bf16: EPI_RES needs a residual");
   if (out_is_f32 && epi != EPI_NONE) return set_error(OMC_ERR_ARG, "omc_gemm_skinny_bf16: fp32 output only with EPI_NONE");
   if (epi == EPI_SWIGLU && (bias != nullptr || N % 2 != 0))

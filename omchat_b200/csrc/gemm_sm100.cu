@@ -267,6 +267,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (p.epi == EPI_GELU) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] = gelu_erf(f[j]);
+          } else if (p.epi == EPI_RELU2) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float z = fmaxf(f[j], 0.f);
+              f[j] = z * z;
+            }
           } else if (p.epi == EPI_RES) {
             if (p.scale != nullptr) {
 #pragma unroll
@@ -490,17 +496,20 @@ extern "C" int omc_gemm_bf16_norm(const void* X, long long ldx, const void* W, l
 // modeling_qwen2_moe.py:307-331): out[r, :] = epi( X[r, :] . W[e(r)]^T ) where the rows of X are sorted by expert, every expert's
 // segment starts on a 128-row tile and tile_expert[r / 128] names the expert (< 0: the tile holds no rows, skipped without
 // touching the weights). W is the experts' matrices stacked, [n_experts * N, K]. One launch, no host knowledge of the routing.
-extern "C" int omc_gemm_bf16_grouped(const void* X, long long ldx, int M_max, const void* W, long long ldw, int n_experts, int N,
-                                     int K, const int32_t* tile_expert, int active_tiles_hint, void* out, long long ldo, int epi,
-                                     void* stream) {
+static int gemm_grouped_impl(const void* X, long long ldx, int M_max, const void* W, long long ldw, int n_experts, int N, int K,
+                             const int32_t* tile_expert, int active_tiles_hint, void* out, long long ldo, int epi, int out_is_f32,
+                             void* stream) {
   if (X == nullptr || W == nullptr || tile_expert == nullptr || out == nullptr)
     return set_error(OMC_ERR_ARG, "omc_gemm_bf16_grouped: null argument");
   if (M_max <= 0 || M_max % kBM != 0 || n_experts <= 0 || N <= 0 || K <= 0 || N % 128 != 0 || K % 8 != 0)
     return set_error(OMC_ERR_SHAPE, "omc_gemm_bf16_grouped: M_max must be whole 128-row tiles, N a multiple of 128, K of 8");
-  if (epi != EPI_NONE && epi != EPI_SWIGLU) return set_error(OMC_ERR_ARG, "omc_gemm_bf16_grouped: epilogue NONE or SWIGLU");
+  if (epi != EPI_NONE && epi != EPI_SWIGLU && epi != EPI_RELU2)
+    return set_error(OMC_ERR_ARG, "omc_gemm_bf16_grouped: epilogue NONE, SWIGLU or RELU2");
+  if (out_is_f32 && epi == EPI_SWIGLU) return set_error(OMC_ERR_ARG, "omc_gemm_bf16_grouped: SwiGLU writes bf16");
   GemmParams p{};
   p.M = M_max; p.N = N; p.K = K;
-  p.out = static_cast<__nv_bfloat16*>(out);
+  if (out_is_f32) p.out_f32 = static_cast<float*>(out);
+  else p.out = static_cast<__nv_bfloat16*>(out);
   p.ldo = ldo;
   p.epi = epi;
   p.grp_tile = tile_expert;
@@ -513,13 +522,25 @@ extern "C" int omc_gemm_bf16_grouped(const void* X, long long ldx, int M_max, co
   return launch_gemm<128, 1>(X, ldx, W, ldw, p, 0, st, n_experts);
 }
 
+extern "C" int omc_gemm_bf16_grouped(const void* X, long long ldx, int M_max, const void* W, long long ldw, int n_experts, int N,
+                                     int K, const int32_t* tile_expert, int active_tiles_hint, void* out, long long ldo, int epi,
+                                     void* stream) {
+  return gemm_grouped_impl(X, ldx, M_max, W, ldw, n_experts, N, K, tile_expert, active_tiles_hint, out, ldo, epi, 0, stream);
+}
+
+extern "C" int omc_gemm_bf16_grouped_f32(const void* X, long long ldx, int M_max, const void* W, long long ldw, int n_experts, int N,
+                                         int K, const int32_t* tile_expert, int active_tiles_hint, float* out, long long ldo, int epi,
+                                         void* stream) {
+  return gemm_grouped_impl(X, ldx, M_max, W, ldw, n_experts, N, K, tile_expert, active_tiles_hint, out, ldo, epi, 1, stream);
+}
+
 static int gemm_impl(const void* X, long long ldx, const void* W, long long ldw, void* out, long long ldo, int M, int N, int K,
                      const void* bias, const void* scale, const void* res, long long ldr, int epi, int out_is_f32,
                      int tile_cfg, const omc_gemm_norm* nf_c, void* stream) {
   omc_gemm_norm* nf = const_cast<omc_gemm_norm*>(nf_c);
   if (M <= 0 || N <= 0 || K <= 0) return set_error(OMC_ERR_SHAPE, "omc_gemm_bf16: empty problem");
   if (N % 8 != 0 || K % 8 != 0) return set_error(OMC_ERR_SHAPE, "omc_gemm_bf16: N and K must be multiples of 8");
-  if (epi < EPI_NONE || epi > EPI_SWIGLU) return set_error(OMC_ERR_ARG, "omc_gemm_bf16: unknown epilogue");
+  if (epi < EPI_NONE || epi > EPI_RELU2) return set_error(OMC_ERR_ARG, "omc_gemm_bf16: unknown epilogue");
   if (epi == EPI_RES && res == nullptr) return set_error(OMC_ERR_ARG, "omc_gemm_bf16: EPI_RES needs a residual");
   if (out_is_f32 && epi != EPI_NONE) return set_error(OMC_ERR_ARG, "omc_gemm_bf16: fp32 output only with EPI_NONE");
   if (epi == EPI_SWIGLU && (bias != nullptr || N % 16 != 0))

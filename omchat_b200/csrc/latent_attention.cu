@@ -44,22 +44,22 @@ __global__ void __launch_bounds__(128) latent_kv_store_kernel(const float* __res
   for (int c = rot_dims + threadIdx.x; c < dr; c += blockDim.x) stf(dst + r + c, row[r + c]);
 }
 
-template <typename TQ>
-__global__ void __launch_bounds__(128) rotary_q_kernel(const float* __restrict__ q32, long long ldq, int H, int dn, int dr,
+template <typename TI, typename TQ>
+__global__ void __launch_bounds__(128) rotary_q_kernel(const TI* __restrict__ q32, long long ldq, int H, int dn, int dr,
                                                        const float* __restrict__ cs, int rot_dims,
                                                        const int32_t* __restrict__ pos, TQ* __restrict__ qcat, int r) {
   const int t = blockIdx.x;
   const float* csr = cs + (long long)pos[t] * rot_dims;
   const int half = rot_dims >> 1;
   for (int h = 0; h < H; ++h) {
-    const float* src = q32 + (long long)t * ldq + (long long)h * (dn + dr) + dn;
+    const TI* src = q32 + (long long)t * ldq + (long long)h * (dn + dr) + dn;
     TQ* dst = qcat + ((long long)t * H + h) * (r + dr) + r;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
-      const float u = src[2 * i], v = src[2 * i + 1], co = csr[2 * i], si = csr[2 * i + 1];
+      const float u = ldf(src + 2 * i), v = ldf(src + 2 * i + 1), co = csr[2 * i], si = csr[2 * i + 1];
       stf(dst + 2 * i, u * co - v * si);
       stf(dst + 2 * i + 1, v * co + u * si);
     }
-    for (int c = rot_dims + threadIdx.x; c < dr; c += blockDim.x) stf(dst + c, src[c]);
+    for (int c = rot_dims + threadIdx.x; c < dr; c += blockDim.x) stf(dst + c, ldf(src + c));
   }
 }
 
@@ -159,14 +159,16 @@ extern "C" int omc_latent_kv_store(const float* dkv, long long ld, int T, int r,
   return check_launch("omc_latent_kv_store");
 }
 
-extern "C" int omc_rotary_q(const float* q32, long long ldq, int T, int H, int dn, int dr, const float* cs, int rot_dims,
+extern "C" int omc_rotary_q(const void* q32, int in_dt, long long ldq, int T, int H, int dn, int dr, const float* cs, int rot_dims,
                             const int32_t* pos, void* qcat, int q_dt, int r, void* stream) {
   if (q32 == nullptr || cs == nullptr || pos == nullptr || qcat == nullptr || T < 0 || H <= 0 || dn < 0 || dr < 0 || rot_dims > dr ||
       (rot_dims & 1))
     return set_error(OMC_ERR_ARG, "omc_rotary_q: bad argument");
   if (T == 0 || dr == 0) return OMC_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  OMC_DT_SWITCH(q_dt, TQ, { rotary_q_kernel<TQ><<<T, 128, 0, st>>>(q32, ldq, H, dn, dr, cs, rot_dims, pos, static_cast<TQ*>(qcat), r); })
+  OMC_DT_SWITCH(in_dt, TI, OMC_DT_SWITCH(q_dt, TQ, {
+    rotary_q_kernel<TI, TQ><<<T, 128, 0, st>>>(static_cast<const TI*>(q32), ldq, H, dn, dr, cs, rot_dims, pos, static_cast<TQ*>(qcat), r);
+  }))
   return check_launch("omc_rotary_q");
 }
 
@@ -229,14 +231,18 @@ struct LatMmaArgs {
   const int32_t* bt;
   const int32_t* items;  // [n][8]: first_row, n_tok, slot, first_pos, key_begin, key_end, part_slot (-1: final), unused
   const float* sink;
-  float* out;
+  void* out;     // [T * H][r] fp32 or bf16
   float* ws_o;   // [part_slot][64][r]
   float* ws_ml;  // [part_slot][64][2]
   int max_pages, page_size, H, r, dr;
   float scale_log2;
+  int two_buffers;  // shared memory holds two key tiles
 };
 
-template <int VS, int NV>  // NV: 8-column output tiles per warp; covers r <= VS * NV * 8
+__device__ __forceinline__ void st_pair(float* p, float x, float y) { *reinterpret_cast<float2*>(p) = make_float2(x, y); }
+__device__ __forceinline__ void st_pair(bf16_t* p, float x, float y) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(x, y); }
+
+template <int VS, int NV, typename TO>  // NV: 8-column output tiles per warp; covers r <= VS * NV * 8
 __global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int D = a.r + a.dr, pitch = D + 8;
@@ -272,11 +278,11 @@ __global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a)
   const int nv0 = vs * nv_per;
   const int32_t* bt = a.bt + (long long)slot * a.max_pages;
   const int k_end = min(ke, first_pos + n_tok);  // exclusive
-  for (int j0 = kb; j0 < k_end; j0 += kMmaKeys) {
-    __syncthreads();  // the previous tile is no longer read
+  // key tiles: with two buffers the next tile is on its way while this one is computed
+  auto stage_keys = [&](bf16_t* buf, int j0) {
     for (int i = tid; i < kMmaKeys * chunks; i += blockDim.x) {
       const int key = i / chunks, c = i - key * chunks;
-      bf16_t* dst = Ks + key * pitch + c * 8;
+      bf16_t* dst = buf + key * pitch + c * 8;
       const int j = j0 + key;
       if (j < k_end) {
         const bf16_t* src = a.pool + ((long long)bt[j / a.page_size] * a.page_size + j % a.page_size) * D + c * 8;
@@ -285,14 +291,31 @@ __global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a)
         *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
       }
     }
-    cp_async_wait_all();
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  bf16_t* Kbuf[2] = {Ks, a.two_buffers ? Ks + kMmaKeys * pitch : Ks};
+  if (kb < k_end) stage_keys(Kbuf[0], kb);
+  int kt = 0;
+  for (int j0 = kb; j0 < k_end; j0 += kMmaKeys, ++kt) {
+    bf16_t* Kc = Kbuf[kt & 1];
+    if (a.two_buffers) {
+      if (j0 + kMmaKeys < k_end) {
+        stage_keys(Kbuf[(kt + 1) & 1], j0 + kMmaKeys);  // that buffer was released by the barrier that ended the previous tile
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+      } else {
+        cp_async_wait_all();
+      }
+    } else {
+      if (kt > 0) stage_keys(Kc, j0);
+      cp_async_wait_all();
+    }
     __syncthreads();
     // S = Q K^T for this warp's 16 rows x 64 keys
     float s[8][4];
 #pragma unroll
     for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
     const uint32_t q_base = smem_u32(Qs + (rg * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * pitch + 8 * (lane >> 4));
-    const uint32_t k_base = smem_u32(Ks + ((lane & 7) + 8 * (lane >> 4)) * pitch + 8 * ((lane >> 3) & 1));
+    const uint32_t k_base = smem_u32(Kc + ((lane & 7) + 8 * (lane >> 4)) * pitch + 8 * ((lane >> 3) & 1));
     for (int kk = 0; kk < D; kk += 16) {
       uint32_t a0, a1, a2, a3;
       ldsm_x4(q_base + kk * 2, a0, a1, a2, a3);
@@ -348,7 +371,7 @@ __global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a)
       o[j][3] *= c1;
     }
     // O += P V over this warp's output tiles (pairs of 8-column tiles per ldmatrix.x4.trans)
-    const uint32_t v_base = smem_u32(Ks + ((lane & 7) + 8 * ((lane >> 3) & 1)) * pitch + 8 * (lane >> 4));
+    const uint32_t v_base = smem_u32(Kc + ((lane & 7) + 8 * ((lane >> 3) & 1)) * pitch + 8 * (lane >> 4));
 #pragma unroll
     for (int kb16 = 0; kb16 < 4; ++kb16) {
       const uint32_t a0 = p[2 * kb16][0], a1 = p[2 * kb16][1], a2 = p[2 * kb16 + 1][0], a3 = p[2 * kb16 + 1][1];
@@ -363,6 +386,7 @@ __global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a)
         }
       }
     }
+    __syncthreads();  // every warp is done with this tile's buffer
   }
   // row sums over the quad
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -376,15 +400,15 @@ __global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a)
       if (row1 < n_rows) d1 += exp2f(a.sink[row1 % a.H] * 1.4426950408889634f - m1);
     }
     const float i0 = 1.f / d0, i1 = 1.f / d1;
-    float* out0 = a.out + ((long long)first_row * a.H + row0) * a.r;
-    float* out1 = a.out + ((long long)first_row * a.H + row1) * a.r;
+    TO* out0 = static_cast<TO*>(a.out) + ((long long)first_row * a.H + row0) * a.r;
+    TO* out1 = static_cast<TO*>(a.out) + ((long long)first_row * a.H + row1) * a.r;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       const int tile = nv0 + j;
       if (j < nv_per && tile < nv) {
         const int col = tile * 8 + 2 * t4;
-        if (row0 < n_rows) *reinterpret_cast<float2*>(out0 + col) = make_float2(o[j][0] * i0, o[j][1] * i0);
-        if (row1 < n_rows) *reinterpret_cast<float2*>(out1 + col) = make_float2(o[j][2] * i1, o[j][3] * i1);
+        if (row0 < n_rows) st_pair(out0 + col, o[j][0] * i0, o[j][1] * i0);
+        if (row1 < n_rows) st_pair(out1 + col, o[j][2] * i1, o[j][3] * i1);
       }
     }
   } else {
@@ -408,52 +432,95 @@ __global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a)
   }
 }
 
-// merges[i] = (first q row = first_row * H, n_rows, first part slot, n_parts): one CTA per group, one warp per row.
+// merges[i] = (first q row = first_row * H, n_rows, first part slot, n_parts): blockIdx.y picks 8 of the group's rows, one warp each.
+constexpr int kMergeMaxParts = 64;
+template <typename TO>
 __global__ void __launch_bounds__(256) latent_attn_merge_kernel(const int32_t* __restrict__ merges, const float* __restrict__ ws_o,
                                                                 const float* __restrict__ ws_ml, const float* __restrict__ sink, int H,
-                                                                int r, float* __restrict__ out) {
+                                                                int r, TO* __restrict__ out) {
+  __shared__ float s_f[8][kMergeMaxParts];
   const int32_t* mg = merges + blockIdx.x * 4;
   const int qrow0 = mg[0], n_rows = mg[1], part0 = mg[2], n_parts = mg[3];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int row = warp; row < n_rows; row += 8) {
-    float mt = -INFINITY;
-    for (int p = 0; p < n_parts; ++p) mt = fmaxf(mt, ws_ml[((long long)(part0 + p) * kMmaRows + row) * 2]);
-    float den = 0.f;
-    for (int p = 0; p < n_parts; ++p) {
-      const float* ml = ws_ml + ((long long)(part0 + p) * kMmaRows + row) * 2;
-      if (ml[0] != -INFINITY) den += ml[1] * exp2f(ml[0] - mt);
-    }
-    if (sink != nullptr) den += exp2f(sink[(qrow0 + row) % H] * 1.4426950408889634f - mt);
-    const float inv = 1.f / den;
-    for (int c = lane; c < r; c += 32) {
-      float v = 0.f;
-      for (int p = 0; p < n_parts; ++p) {
-        const float mp = ws_ml[((long long)(part0 + p) * kMmaRows + row) * 2];
-        if (mp != -INFINITY) v += ws_o[((long long)(part0 + p) * kMmaRows + row) * r + c] * exp2f(mp - mt);
-      }
-      out[((long long)qrow0 + row) * r + c] = v * inv;
-    }
+  const int row = blockIdx.y * 8 + warp;
+  if (row >= n_rows) return;
+  // factors exp2(m_p - m) / denominator of every part, computed once per row
+  float mt = -INFINITY;
+  for (int p = lane; p < n_parts; p += 32) mt = fmaxf(mt, ws_ml[((long long)(part0 + p) * kMmaRows + row) * 2]);
+  mt = seq_warp_max(mt);
+  const float sk = sink != nullptr ? sink[(qrow0 + row) % H] * 1.4426950408889634f : -INFINITY;
+  mt = fmaxf(mt, sk);
+  float den = 0.f;
+  for (int p = lane; p < n_parts; p += 32) {
+    const float* ml = ws_ml + ((long long)(part0 + p) * kMmaRows + row) * 2;
+    const float f = ml[0] == -INFINITY ? 0.f : exp2f(ml[0] - mt);
+    s_f[warp][p] = f;
+    den += ml[1] * f;
+  }
+  den = seq_warp_sum(den);
+  if (sink != nullptr) den += exp2f(sk - mt);
+  const float inv = 1.f / den;
+  __syncwarp();
+  for (int c = lane; c < r; c += 32) {
+    float v = 0.f;
+    for (int p = 0; p < n_parts; ++p) v = fmaf(ws_o[((long long)(part0 + p) * kMmaRows + row) * r + c], s_f[warp][p], v);
+    stf(out + ((long long)qrow0 + row) * r + c, v * inv);
   }
 }
 
-template <int VS, int NV>
-static int launch_lat_mma(const LatMmaArgs& a, int n_items, size_t smem, cudaStream_t st) {
+// Work list of a decode-only step written on the device (so that the step can be replayed from a CUDA graph while the contexts
+// grow): row b at position pos[b] sees pos[b] + 1 keys, cut into `parts` ranges of whole 64-key tiles (ranges past the end stay
+// empty and contribute nothing to the merge).
+__global__ void latent_decode_items_kernel(const int32_t* __restrict__ pos, const int32_t* __restrict__ slot, int B, int H, int parts,
+                                           int32_t* __restrict__ items, int32_t* __restrict__ merges) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= B * parts) return;
+  const int b = i / parts, j = i - b * parts;
+  const int keys = pos[b] + 1;
+  const int span = ((keys + parts - 1) / parts + kMmaKeys - 1) / kMmaKeys * kMmaKeys;
+  int32_t* it = items + (long long)i * 8;
+  it[0] = b;
+  it[1] = 1;
+  it[2] = slot[b];
+  it[3] = pos[b];
+  it[4] = min(j * span, keys);
+  it[5] = min((j + 1) * span, keys);
+  it[6] = parts > 1 ? i : -1;
+  it[7] = 0;
+  if (j == 0 && parts > 1) {
+    int32_t* mg = merges + b * 4;
+    mg[0] = b * H;
+    mg[1] = H;
+    mg[2] = b * parts;
+    mg[3] = parts;
+  }
+}
+
+template <int VS, int NV, typename TO>
+static int launch_lat_mma_t(const LatMmaArgs& a, int n_items, size_t smem, cudaStream_t st) {
   static bool attr_done[kMaxDevices] = {};
   const int dev = cur_device();
   if (!attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(latent_attn_mma_kernel<VS, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(latent_attn_mma_kernel<VS, NV, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return set_error(OMC_ERR_CUDA, cudaGetErrorString(e));
     attr_done[dev] = true;
   }
-  latent_attn_mma_kernel<VS, NV><<<n_items, 128 * VS, smem, st>>>(a);
+  latent_attn_mma_kernel<VS, NV, TO><<<n_items, 128 * VS, smem, st>>>(a);
   return check_launch("omc_latent_attn_mma");
+}
+
+template <int VS, int NV>
+static int launch_lat_mma(const LatMmaArgs& a, int out_dt, int n_items, size_t smem, cudaStream_t st) {
+  if (out_dt == OMC_DT_BF16) return launch_lat_mma_t<VS, NV, bf16_t>(a, n_items, smem, st);
+  return launch_lat_mma_t<VS, NV, float>(a, n_items, smem, st);
 }
 
 }  // namespace omc
 
 extern "C" int omc_latent_attn_mma(const void* qcat, int T, int H, int r, int dr, const void* pool, const int32_t* block_table,
                                    int max_pages, int page_size, const int32_t* items, int n_items, const int32_t* merges,
-                                   int n_merges, const float* sink, float scale, float* out, float* ws_o, float* ws_ml, void* stream) {
+                                   int n_merges, const float* sink, float scale, void* out, int out_dt, float* ws_o, float* ws_ml,
+                                   void* stream) {
   if (qcat == nullptr || pool == nullptr || block_table == nullptr || items == nullptr || out == nullptr || T < 0 || H <= 0 ||
       page_size <= 0 || max_pages <= 0 || n_items < 0 || n_merges < 0 || (n_merges > 0 && (merges == nullptr || ws_o == nullptr || ws_ml == nullptr)))
     return set_error(OMC_ERR_ARG, "omc_latent_attn_mma: bad argument");
@@ -461,17 +528,37 @@ extern "C" int omc_latent_attn_mma(const void* qcat, int T, int H, int r, int dr
     return set_error(OMC_ERR_SHAPE, "omc_latent_attn_mma: latent width a multiple of 16 up to 512, rotated width a multiple of 16, at most 64 heads");
   if (n_items == 0) return OMC_OK;
   const int D = r + dr;
-  const size_t smem = (size_t)(kMmaRows + kMmaKeys) * (D + 8) * sizeof(bf16_t);
+  size_t smem = (size_t)(kMmaRows + 2 * kMmaKeys) * (D + 8) * sizeof(bf16_t);
+  int two = 1;
+  if (smem > 227 * 1024) {
+    two = 0;
+    smem = (size_t)(kMmaRows + kMmaKeys) * (D + 8) * sizeof(bf16_t);
+  }
   if (smem > 227 * 1024) return set_error(OMC_ERR_SHAPE, "omc_latent_attn_mma: rows too wide for shared memory");
   LatMmaArgs a{static_cast<const bf16_t*>(qcat), static_cast<const bf16_t*>(pool), block_table, items, sink, out, ws_o, ws_ml,
-               max_pages, page_size, H, r, dr, scale * 1.4426950408889634f};
+               max_pages, page_size, H, r, dr, scale * 1.4426950408889634f, two};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int rc;
-  if (r <= 64) rc = launch_lat_mma<1, 8>(a, n_items, smem, st);
-  else if (r <= 128) rc = launch_lat_mma<1, 16>(a, n_items, smem, st);
-  else if (r <= 256) rc = launch_lat_mma<2, 16>(a, n_items, smem, st);
-  else rc = launch_lat_mma<2, 32>(a, n_items, smem, st);
+  if (out_dt != OMC_DT_F32 && out_dt != OMC_DT_BF16) return set_error(OMC_ERR_ARG, "omc_latent_attn_mma: unknown output dtype");
+  if (r <= 64) rc = launch_lat_mma<1, 8>(a, out_dt, n_items, smem, st);
+  else if (r <= 128) rc = launch_lat_mma<1, 16>(a, out_dt, n_items, smem, st);
+  else if (r <= 256) rc = launch_lat_mma<2, 16>(a, out_dt, n_items, smem, st);
+  else rc = launch_lat_mma<2, 32>(a, out_dt, n_items, smem, st);
   if (rc != OMC_OK || n_merges == 0) return rc;
-  latent_attn_merge_kernel<<<n_merges, 256, 0, st>>>(merges, ws_o, ws_ml, sink, H, r, out);
+  if (out_dt == OMC_DT_BF16)
+    latent_attn_merge_kernel<bf16_t><<<dim3(n_merges, kMmaRows / 8), 256, 0, st>>>(merges, ws_o, ws_ml, sink, H, r, static_cast<bf16_t*>(out));
+  else
+    latent_attn_merge_kernel<float><<<dim3(n_merges, kMmaRows / 8), 256, 0, st>>>(merges, ws_o, ws_ml, sink, H, r, static_cast<float*>(out));
   return check_launch("omc_latent_attn_merge");
+}
+
+extern "C" int omc_latent_decode_items(const int32_t* pos, const int32_t* slot, int B, int H, int parts, int32_t* items, int32_t* merges,
+                                       void* stream) {
+  if (pos == nullptr || slot == nullptr || items == nullptr || B < 0 || H <= 0 || parts <= 0 || parts > kMergeMaxParts ||
+      (parts > 1 && merges == nullptr))
+    return set_error(OMC_ERR_ARG, "omc_latent_decode_items: bad argument");
+  if (B == 0) return OMC_OK;
+  const int n = B * parts;
+  latent_decode_items_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(pos, slot, B, H, parts, items, merges);
+  return check_launch("omc_latent_decode_items");
 }

@@ -82,6 +82,102 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(LinearArgs a) {
   }
 }
 
+// ---- bf16 x bf16 on the tensor pipe (mma.sync.m16n8k16): the same contract for operands whose rows start on 16-byte boundaries.
+// 128 x 128 output tile, K slices of 32 double-buffered with cp.async, 8 warps of 64 x 32. It serves the batched per-head products
+// of latent attention (absorbing W_uk into the query, W_uv after the attention), whose heads are column slices of one buffer.
+constexpr int kMmaBM = 128, kMmaBN = 128, kMmaBK = 32, kMmaPitch = kMmaBK + 8;
+
+__device__ __forceinline__ uint32_t lin_smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+template <typename TY>
+__global__ void __launch_bounds__(256) linear_mma_kernel(LinearArgs a) {
+  __shared__ __align__(16) bf16_t As[2][kMmaBM * kMmaPitch];
+  __shared__ __align__(16) bf16_t Bs[2][kMmaBN * kMmaPitch];
+  const int m0 = blockIdx.y * kMmaBM, n0 = blockIdx.x * kMmaBN;
+  const bf16_t* X = static_cast<const bf16_t*>(a.X) + (long long)blockIdx.z * a.sx;
+  const bf16_t* W = static_cast<const bf16_t*>(a.W) + (long long)blockIdx.z * a.sw;
+  TY* Y = static_cast<TY*>(a.Y) + (long long)blockIdx.z * a.sy;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wm = warp >> 2, wn = warp & 3;  // 2 x 4 warps: rows wm * 64, columns wn * 32
+  float acc[4][4][4] = {};
+  auto stage = [&](int buf, int k0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int idx = tid + i * 256;          // 512 chunks of 8 elements per operand tile
+      const int row = idx >> 2, c = (idx & 3) * 8;
+      const int k = k0 + c;
+      bf16_t* da = &As[buf][row * kMmaPitch + c];
+      bf16_t* db = &Bs[buf][row * kMmaPitch + c];
+      if (m0 + row < a.M && k < a.K)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(lin_smem_u32(da)), "l"(X + (long long)(m0 + row) * a.ldx + k));
+      else *reinterpret_cast<uint4*>(da) = make_uint4(0, 0, 0, 0);
+      if (n0 + row < a.N && k < a.K)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(lin_smem_u32(db)), "l"(W + (long long)(n0 + row) * a.ldw + k));
+      else *reinterpret_cast<uint4*>(db) = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int nk = (a.K + kMmaBK - 1) / kMmaBK;
+  stage(0, 0);
+  for (int kt = 0; kt < nk; ++kt) {
+    const int buf = kt & 1;
+    if (kt + 1 < nk) {
+      stage(buf ^ 1, (kt + 1) * kMmaBK);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kMmaBK; kk += 16) {
+      uint32_t bfr[4][2];
+#pragma unroll
+      for (int nn = 0; nn < 2; ++nn) {  // two 8-column tiles per ldmatrix.x4
+        const bf16_t* pb = &Bs[buf][(wn * 32 + nn * 16 + (lane & 7) + 8 * (lane >> 4)) * kMmaPitch + kk + 8 * ((lane >> 3) & 1)];
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(bfr[2 * nn][0]), "=r"(bfr[2 * nn][1]), "=r"(bfr[2 * nn + 1][0]), "=r"(bfr[2 * nn + 1][1])
+                     : "r"(lin_smem_u32(pb)));
+      }
+#pragma unroll
+      for (int mm = 0; mm < 4; ++mm) {
+        uint32_t a0, a1, a2, a3;
+        const bf16_t* pa = &As[buf][(wm * 64 + mm * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * kMmaPitch + kk + 8 * (lane >> 4)];
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(lin_smem_u32(pa)));
+#pragma unroll
+        for (int nn = 0; nn < 4; ++nn)
+          asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                       : "+f"(acc[mm][nn][0]), "+f"(acc[mm][nn][1]), "+f"(acc[mm][nn][2]), "+f"(acc[mm][nn][3])
+                       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bfr[nn][0]), "r"(bfr[nn][1]));
+      }
+    }
+    __syncthreads();
+  }
+  const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+  for (int mm = 0; mm < 4; ++mm)
+#pragma unroll
+    for (int nn = 0; nn < 4; ++nn)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int m = m0 + wm * 64 + mm * 16 + g + 8 * (e >> 1);
+        const int n = n0 + wn * 32 + nn * 8 + 2 * t4 + (e & 1);
+        if (m < a.M && n < a.N) stf(Y + (long long)m * a.ldy + n, apply_act(acc[mm][nn][e] * a.alpha, a.act));
+      }
+}
+
+static bool mma_operands_ok(const LinearArgs& a) {
+  return a.tile_group == nullptr && a.K % 8 == 0 && a.ldx % 8 == 0 && a.ldw % 8 == 0 && a.sx % 8 == 0 && a.sw % 8 == 0 &&
+         reinterpret_cast<uintptr_t>(a.X) % 16 == 0 && reinterpret_cast<uintptr_t>(a.W) % 16 == 0;
+}
+
+static int launch_linear_mma(const LinearArgs& a, int y_dt, int batch, cudaStream_t st) {
+  dim3 grid((a.N + kMmaBN - 1) / kMmaBN, (a.M + kMmaBM - 1) / kMmaBM, batch);
+  if (y_dt == OMC_DT_F32) linear_mma_kernel<float><<<grid, 256, 0, st>>>(a);
+  else if (y_dt == OMC_DT_BF16) linear_mma_kernel<bf16_t><<<grid, 256, 0, st>>>(a);
+  else return set_error(OMC_ERR_ARG, "omc_linear: unknown output dtype");
+  return check_launch("omc_linear");
+}
+
 template <typename TX, typename TW>
 static int launch_linear(const LinearArgs& a, int y_dt, int batch, cudaStream_t st) {
   dim3 grid((a.N + kLinBN - 1) / kLinBN, (a.M + kLinBM - 1) / kLinBM, batch);
@@ -107,6 +203,10 @@ extern "C" int omc_linear(const void* X, int x_dt, long long ldx, long long sx, 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (x_dt == OMC_DT_F32 && w_dt == OMC_DT_F32) return launch_linear<float, float>(a, y_dt, batch, st);
   if (x_dt == OMC_DT_F32 && w_dt == OMC_DT_BF16) return launch_linear<float, bf16_t>(a, y_dt, batch, st);
-  if (x_dt == OMC_DT_BF16 && w_dt == OMC_DT_BF16) return launch_linear<bf16_t, bf16_t>(a, y_dt, batch, st);
+  if (x_dt == OMC_DT_BF16 && w_dt == OMC_DT_BF16) {
+    // the choice depends on layout and widths only, never on M: a row is computed by the same kernel in every batch
+    if (mma_operands_ok(a) && (long long)N * K >= 4096) return launch_linear_mma(a, y_dt, batch, st);
+    return launch_linear<bf16_t, bf16_t>(a, y_dt, batch, st);
+  }
   return set_error(OMC_ERR_ARG, "omc_linear: operand dtypes must be (f32, f32), (f32, bf16) or (bf16, bf16)");
 }

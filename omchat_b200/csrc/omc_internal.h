@@ -6,7 +6,7 @@
 
 namespace omc {
 
-enum { EPI_NONE = OMC_EPI_NONE, EPI_GELU = OMC_EPI_GELU, EPI_RES = OMC_EPI_RES, EPI_SWIGLU = OMC_EPI_SWIGLU };
+enum { EPI_NONE = OMC_EPI_NONE, EPI_GELU = OMC_EPI_GELU, EPI_RES = OMC_EPI_RES, EPI_SWIGLU = OMC_EPI_SWIGLU, EPI_RELU2 = OMC_EPI_RELU2 };
 
 // records the message for omc_last_error() and returns `code`
 int set_error(int code, const char* msg);

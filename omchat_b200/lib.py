@@ -15,7 +15,7 @@ import torch
 _PKG = Path(__file__).resolve().parent
 LIB_PATH = _PKG / "_lib" / "libomchat_b200.so"
 
-EPI_NONE, EPI_GELU, EPI_RES, EPI_SWIGLU = 0, 1, 2, 3
+EPI_NONE, EPI_GELU, EPI_RES, EPI_SWIGLU, EPI_RELU2 = 0, 1, 2, 3, 4
 
 # every symbol include/omchat_b200.h declares: name -> (restype, argtypes)
 _P, _I, _L, _F = c_void_p, c_int, c_longlong, c_float
@@ -47,6 +47,7 @@ SIGNATURES = {
     "omc_moe_plan": (_I, [_P, _I, _I, _P, _P, _P, _P]),
     "omc_moe_scatter": (_I, [_P, _L, _I, _I, _P, _I, _P, _P, _P, _L, _P, _P]),
     "omc_gemm_bf16_grouped": (_I, [_P, _L, _I, _P, _L, _I, _I, _I, _P, _I, _P, _L, _I, _P]),
+    "omc_gemm_bf16_grouped_f32": (_I, [_P, _L, _I, _P, _L, _I, _I, _I, _P, _I, _P, _L, _I, _P]),
     "omc_moe_combine": (_I, [_P, _L, _I, _I, _P, _L, _P, _P, _I, _P, _L, _P, _P, _I, _P]),
     "omc_moe_plan_scatter": (_I, [_P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _P, _I, _P, _L, _P, _P]),
     "omc_vit_im2col": (_I, [_P, _I, _P, _L, _I, _I, _I, _P]),
@@ -286,6 +287,20 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
                               _ptr(bias), _ptr(scale), _ptr(res), res.stride(0) if res is not None else 0, epi,
                               1 if out_f32 else 0, tile_cfg, _stream())
     _check(rc, "omc_gemm_bf16")
+    return out
+
+
+def gemm_grouped(x: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, out: torch.Tensor, epi: int = EPI_NONE,
+                 active_tiles_hint: int = 0) -> torch.Tensor:
+    """out[r] = epi(x[r] @ w[tile_expert[r // 128]]^T): x [M_max, K] expert-sorted rows in whole 128-row tiles, w [E, N, K]
+    stacked expert matrices, out [M_max, N] bf16 or fp32 (omc_gemm_bf16_grouped / _f32)."""
+    _need_cuda(x, w, tile_expert, out)
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.dim() == 3 and w.is_contiguous() and x.stride(1) == 1
+    E, N, K = w.shape
+    fn = load().omc_gemm_bf16_grouped_f32 if out.dtype == torch.float32 else load().omc_gemm_bf16_grouped
+    rc = fn(_ptr(x), x.stride(0), x.shape[0], _ptr(w), K, E, N, K, _ptr(tile_expert), active_tiles_hint, _ptr(out), out.stride(0),
+            epi, _stream())
+    _check(rc, "omc_gemm_bf16_grouped")
     return out
 
 

@@ -47,7 +47,7 @@ class LatentAttnW:
 
 @dataclass
 class RouterMoeW:
-    router_cat: torch.Tensor            # [E_tot (+ 1), C]: router rows, then the shared expert's gate row
+    router_cat: torch.Tensor            # [E_tot (+ 1) rounded up to 8, C]: router rows, the shared expert's gate row, zero rows
     correction: Optional[torch.Tensor]  # fp32 [E_tot]
     up: Optional[torch.Tensor]          # [E, ff, C]
     down: Optional[torch.Tensor]        # [E, C, ff]
@@ -103,6 +103,9 @@ def weights_from_state_dict(sd: Dict[str, torch.Tensor], cfg: VoduzenConfig, dev
             rows = [router]
             if s.shared_ff:
                 rows.append(g(q + "shared.sg").view(1, -1))
+            n_rows = sum(x.shape[0] for x in rows)
+            if n_rows % 8:   # zero rows up to a multiple of 8: the tensor-core GEMMs take the matrix, the extra logits are never read
+                rows.append(torch.zeros(8 - n_rows % 8, router.shape[1], device=device, dtype=dtype))
             mlp = RouterMoeW(
                 router_cat=torch.cat(rows, dim=0).contiguous(),
                 correction=g(q + "correction", torch.float32) if (q + "correction") in sd else None,
@@ -161,7 +164,10 @@ def random_state_dict(cfg: VoduzenConfig, seed: int = 0, std: float = 0.05) -> D
 # ------------------------------------------------------------------------------------------------------------------- decoder
 # Matrices with at least this many elements go through the tcgen05 GEMM of the core library when the operands are bf16 and the
 # dimensions are multiples of 8; below it a launch is latency-bound either way and the FMA kernel needs no second library.
+# Steps of up to 64 rows stream the weights through the skinny GEMM from a much smaller size on: the FMA kernel walks K with one
+# 64-row tile per CTA, which leaves a decode step waiting on a handful of CTAs.
 TENSOR_GEMM_MIN_WEIGHT = 1 << 20
+SKINNY_GEMM_MIN_WEIGHT = 1 << 17
 
 
 class VoduzenDecoder:
@@ -173,6 +179,9 @@ class VoduzenDecoder:
         self.tensor_gemm = dtype == torch.bfloat16
         self.tensor_attention = True    # False: the plain attention kernel for every shape (A/B, tests)
         self._moe_ws = {}
+        self._decode_plans = {}   # (rows, heads, parts) -> seqlib.DecodeAttnPlan
+        self._graphs = {}         # (rows, parts, id(cache)) -> captured decode-only step
+        self.use_graph = True
 
     # ---- cache
     def cache_widths(self) -> List[int]:
@@ -198,9 +207,11 @@ class VoduzenDecoder:
         """act(alpha * x @ w^T) -> [rows, N] of out_dtype."""
         M, K = x.shape
         N = w.shape[0]
-        if (self.tensor_gemm and act == seqlib.ACT_NONE and alpha == 1.0 and x.dtype == torch.bfloat16 and N * K >= TENSOR_GEMM_MIN_WEIGHT
-                and N % 8 == 0 and K % 8 == 0 and x.stride(0) % 8 == 0):
-            return lib.gemm(x, w, out_f32=out_dtype == torch.float32)
+        big = N * K >= (SKINNY_GEMM_MIN_WEIGHT if M <= lib.SKINNY_MAX_M else TENSOR_GEMM_MIN_WEIGHT)
+        if (self.tensor_gemm and x.dtype == torch.bfloat16 and big and N % 8 == 0 and K % 8 == 0
+                and x.stride(0) % 8 == 0 and (act == seqlib.ACT_NONE or (act == seqlib.ACT_RELU2 and out_dtype == torch.bfloat16))):
+            y = lib.gemm(x, w, out_f32=out_dtype == torch.float32, epi=lib.EPI_RELU2 if act == seqlib.ACT_RELU2 else lib.EPI_NONE)
+            return y if alpha == 1.0 else y.mul_(alpha)
         out = torch.empty(M, N, device=x.device, dtype=out_dtype)
         return seqlib.linear(x, w, out, alpha=alpha, act=act)
 
@@ -211,27 +222,38 @@ class VoduzenDecoder:
         T = xb.shape[0]
         H, dn, dr, dv, r = spec.heads, spec.dim, spec.rot_dim, spec.vdim, spec.kv_rank
         f32 = torch.float32
+        # bf16: q, the absorbed query and the weighted latent sum are bf16 matrix operands (tensor-pipe GEMMs on both sides);
+        # fp32: they stay fp32 throughout
+        qdt = self.dtype
         if spec.q_rank is not None:
             cq32 = self._linear(xb, mw.dq, f32)
             cq = seqlib.rms_rows(cq32, mw.dq_norm, self.eps, torch.empty(T, spec.q_rank, device=xb.device, dtype=self.dtype))
-            q32 = self._linear(cq, mw.uq, f32)
+            q = self._linear(cq, mw.uq, qdt)
         else:
-            q32 = self._linear(xb, mw.q, f32)
+            q = self._linear(xb, mw.q, qdt)
         dkv32 = self._linear(xb, mw.dkv, f32)
         cs = self._rot_table(mw, spec, cache.capacity)
         pool = cache.pools[li]
         seqlib.latent_kv_store(dkv32, r, dr, mw.dkv_norm, self.eps, cs, spec.rot.dims, pos, slot, cache.block_table,
                                cache.page_size, pool)
         qcat = torch.empty(T, H, r + dr, device=xb.device, dtype=self.dtype)
-        seqlib.rotary_q(q32, H, dn, dr, cs, spec.rot.dims, pos, qcat, r)
-        # absorbed keys: qcat[t, h, :r] = q32[t, h, :dn] @ W_uk,h  (one problem per head, column slices of both buffers)
-        seqlib.linear(q32, mw.uk_t, qcat, M=T, N=r, K=dn, ldx=q32.stride(0), sx=dn + dr, ldw=dn, sw=r * dn, ldy=H * (r + dr),
+        seqlib.rotary_q(q, H, dn, dr, cs, spec.rot.dims, pos, qcat, r)
+        # absorbed keys: qcat[t, h, :r] = q[t, h, :dn] @ W_uk,h  (one problem per head, column slices of both buffers)
+        seqlib.linear(q, mw.uk_t, qcat, M=T, N=r, K=dn, ldx=q.stride(0), sx=dn + dr, ldw=dn, sw=r * dn, ldy=H * (r + dr),
                       sy=r + dr, batch=H)
-        olat = torch.empty(T, H, r, device=xb.device, dtype=f32)
-        if plans is not None and self.tensor_attention and seqlib.latent_attn_mma_ok(H, r, dr, self.dtype):
+        use_mma = plans is not None and self.tensor_attention and seqlib.latent_attn_mma_ok(H, r, dr, self.dtype)
+        olat = torch.empty(T, H, r, device=xb.device, dtype=self.dtype if use_mma else f32)
+        if use_mma:
             plan = plans.get(H)
             if plan is None:
-                plan = plans[H] = seqlib.LatentAttnPlan(plans["portions"], H, xb.device)
+                if "decode_parts" in plans:       # decode-only step: the list is written on the device from pos / slot
+                    plan = self._decode_plans.get((T, H, plans["decode_parts"]))
+                    if plan is None:
+                        plan = self._decode_plans[(T, H, plans["decode_parts"])] = seqlib.DecodeAttnPlan(T, H, plans["decode_parts"], xb.device)
+                    plan.fill(pos, slot)
+                else:
+                    plan = seqlib.LatentAttnPlan(plans["portions"], H, xb.device)
+                plans[H] = plan
             seqlib.latent_attn_mma(qcat, r, dr, pool, cache.block_table, cache.page_size, plan, mw.sink, spec.scale, olat)
         else:
             seqlib.latent_attn(qcat, r, dr, pool, cache.block_table, cache.page_size, pos, slot, mw.sink, spec.scale, olat)
@@ -243,15 +265,20 @@ class VoduzenDecoder:
     class _MoeWs:
         pass
 
-    def _moe_workspace(self, T: int, s: RouterMoeSpec):
+    def _grouped_tensor_gemm(self, s: RouterMoeSpec) -> bool:
+        """Experts on the grouped tcgen05 GEMM (128-row tiles): bf16, tile-aligned widths, matrices large enough to matter."""
+        return (self.tensor_gemm and s.experts > 0 and s.expert_ff % 128 == 0 and self.C % 128 == 0
+                and s.expert_ff * self.C >= TENSOR_GEMM_MIN_WEIGHT // 4)
+
+    def _moe_workspace(self, T: int, s: RouterMoeSpec, tile: int):
         bucket = 1 << max(T - 1, 0).bit_length()
-        key = (bucket, s.experts, s.identity, s.top, s.expert_ff)
+        key = (bucket, s.experts, s.identity, s.top, s.expert_ff, tile)
         ws = self._moe_ws.get(key)
         if ws is None:
             dev, i32 = self.device, torch.int32
             ws = VoduzenDecoder._MoeWs()
-            ws.max_tiles = seqlib.moe_max_tiles(bucket, s.top, max(s.experts, 1))
-            rows = ws.max_tiles * seqlib.LINEAR_TILE
+            ws.max_tiles = seqlib.moe_max_tiles(bucket, s.top, max(s.experts, 1), tile)
+            rows = ws.max_tiles * tile
             ws.ids = torch.empty(bucket, s.top, device=dev, dtype=i32)
             ws.w = torch.empty(bucket, s.top, device=dev, dtype=torch.float32)
             ws.gate = torch.empty(bucket, device=dev, dtype=torch.float32)
@@ -270,22 +297,28 @@ class VoduzenDecoder:
         """The feed-forward half of layer li, its output norm and the residual add: updates h32 (and xb_out) in place."""
         s, mw, lw = self.cfg.layers[li].mlp, self.w.layers[li].mlp, self.w.layers[li]
         T = xb.shape[0]
-        ws = self._moe_workspace(T, s)
+        grouped = self._grouped_tensor_gemm(s)
+        tile = 128 if grouped else seqlib.LINEAR_TILE
+        ws = self._moe_workspace(T, s, tile)
         e_tot = s.experts + s.identity
         z32 = self._linear(xb, mw.router_cat, torch.float32)
         has_gate = s.shared_ff is not None
         seqlib.router_topk(z32, e_tot, s.experts, s.top, mw.correction, has_gate, ws.ids, ws.w, ws.gate, ws.counts)
         ys = None
         if s.experts:
-            tile = seqlib.LINEAR_TILE
-            max_tiles = seqlib.moe_max_tiles(T, s.top, s.experts)
+            max_tiles = seqlib.moe_max_tiles(T, s.top, s.experts, tile)
             seqlib.moe_plan_tiles(ws.counts, s.experts, tile, max_tiles, ws.seg_start, ws.cursor, ws.tile_group)
             seqlib.moe_scatter_rows(xb, ws.ids, s.top, s.experts, ws.seg_start, ws.cursor, ws.slot_of, ws.xs)
             rows = max_tiles * tile
-            seqlib.linear(ws.xs, mw.up, ws.act, M=rows, N=s.expert_ff, K=self.C, ldw=self.C, act=seqlib.ACT_RELU2,
-                          tile_group=ws.tile_group, group_stride=s.expert_ff * self.C)
-            seqlib.linear(ws.act, mw.down, ws.ys, M=rows, N=self.C, K=s.expert_ff, ldw=s.expert_ff, tile_group=ws.tile_group,
-                          group_stride=self.C * s.expert_ff)
+            if grouped:
+                hint = min(max_tiles, T * s.top)
+                lib.gemm_grouped(ws.xs[:rows], mw.up, ws.tile_group, ws.act[:rows], lib.EPI_RELU2, hint)
+                lib.gemm_grouped(ws.act[:rows], mw.down, ws.tile_group, ws.ys[:rows], lib.EPI_NONE, hint)
+            else:
+                seqlib.linear(ws.xs, mw.up, ws.act, M=rows, N=s.expert_ff, K=self.C, ldw=self.C, act=seqlib.ACT_RELU2,
+                              tile_group=ws.tile_group, group_stride=s.expert_ff * self.C)
+                seqlib.linear(ws.act, mw.down, ws.ys, M=rows, N=self.C, K=s.expert_ff, ldw=s.expert_ff, tile_group=ws.tile_group,
+                              group_stride=self.C * s.expert_ff)
             ys = ws.ys
         else:
             ws.slot_of.fill_(-1)
@@ -299,7 +332,7 @@ class VoduzenDecoder:
     @torch.no_grad()
     def step(self, tokens: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor, cache: PagedLatentCache,
              want_rows: Optional[torch.Tensor] = None, collect: Optional[list] = None,
-             portions: Optional[Sequence] = None) -> Optional[torch.Tensor]:
+             portions: Optional[Sequence] = None, decode_parts: Optional[int] = None) -> Optional[torch.Tensor]:
         """tokens / pos / slot: int32 [T] on the device - row t is token tokens[t] at position pos[t] of the request in cache
         slot slot[t]; rows of one request are consecutive and ascending in position. Appends every row to the cache and returns
         fp32 logits [len(want_rows), vocab] (None when no row is asked for). collect: receives the residual stream after
@@ -308,6 +341,8 @@ class VoduzenDecoder:
         T = tokens.numel()
         dev = self.device
         plans = {"portions": list(portions)} if portions is not None else None
+        if decode_parts is not None:   # every row is a single decoded token of its own request
+            plans = {"decode_parts": decode_parts}
         h32 = torch.empty(T, self.C, device=dev, dtype=torch.float32)
         xb = torch.empty(T, self.C, device=dev, dtype=self.dtype)
         seqlib.embed_scale(tokens, self.w.embed, self.cfg.embedding_scale, h32, xb)
@@ -324,6 +359,52 @@ class VoduzenDecoder:
         xf = seqlib.rms_rows(hw, self.w.final_norm, self.eps, torch.empty(hw.shape[0], self.C, device=dev, dtype=self.dtype),
                              one_plus=True)
         return self._linear(xf, self.w.head, torch.float32, alpha=self.cfg.logit_scale)
+
+
+    class _Graph:
+        pass
+
+    @torch.no_grad()
+    def decode_step(self, meta_host: torch.Tensor, cache: PagedLatentCache, max_keys: int) -> torch.Tensor:
+        """A decode-only step: meta_host int32 [3, B] (tokens, positions, slots; pinned host memory), one row per request.
+        The step is captured once per (B, key-range count, cache) in a CUDA graph and replayed: embedding, all layers against
+        the cache (the attention work list is rebuilt on the device from the positions) and the logits of all B rows.
+        Returns fp32 logits [B, vocab] (a static buffer, overwritten by the next call)."""
+        B = meta_host.shape[1]
+        parts = seqlib.DecodeAttnPlan.parts_for(B, max_keys)
+        key = (B, parts, id(cache))
+        g = self._graphs.get(key)
+        if g is not None and g.cache is not cache:
+            g = None
+        if g is None:
+            if len(self._graphs) >= 16:
+                self._graphs.pop(next(iter(self._graphs)))
+            g = VoduzenDecoder._Graph()
+            g.cache = cache
+            g.meta = torch.zeros(3, B, device=self.device, dtype=torch.int32)
+            g.want = torch.arange(B, device=self.device)
+            g.meta.copy_(meta_host, non_blocking=True)
+            if not self.use_graph:
+                g.graph = None
+            else:
+                # one eager run first: workspaces, rotary tables and kernel attributes are set up outside the capture (it writes
+                # the same cache rows the replay writes again)
+                self.step(g.meta[0], g.meta[1], g.meta[2], cache, g.want, decode_parts=parts)
+                torch.cuda.synchronize()
+                n0 = lib.launch_count()
+                g.graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g.graph):
+                    g.logits = self.step(g.meta[0], g.meta[1], g.meta[2], cache, g.want, decode_parts=parts)
+                g.launches = lib.launch_count() - n0
+                lib.add_launches(-g.launches)   # the capture does not execute
+            self._graphs[key] = g
+        else:
+            g.meta.copy_(meta_host, non_blocking=True)
+        if g.graph is None:
+            return self.step(g.meta[0], g.meta[1], g.meta[2], cache, g.want, decode_parts=parts)
+        g.graph.replay()
+        lib.add_launches(g.launches)
+        return g.logits
 
 
 # ------------------------------------------------------------------------------------------------------------------- model
@@ -365,6 +446,11 @@ class VoduzenForCausalLM:
     def step(self, tokens, pos, slot, cache, want_rows=None, collect=None, portions=None):
         with torch.cuda.device(self.device):
             return self.decoder.step(tokens, pos, slot, cache, want_rows, collect, portions)
+
+    def decode_step(self, meta_host, cache, max_keys: int):
+        """Decode-only batch (one token per request) through the captured CUDA graph; see VoduzenDecoder.decode_step."""
+        with torch.cuda.device(self.device):
+            return self.decoder.decode_step(meta_host, cache, max_keys)
 
     @torch.no_grad()
     def generate(self, input_ids, max_new_tokens: int = 32, eos_token_id: Optional[int] = None, do_sample: bool = False,

@@ -27,9 +27,10 @@ SIGNATURES = {
     "omc_rms_rows": (_I, [_P, _L, _P, _I, _I, _F, _P, _I, _L, _I, _I, _P]),
     "omc_norm_residual": (_I, [_P, _L, _P, _I, _F, _P, _L, _P, _I, _L, _I, _I, _P]),
     "omc_latent_kv_store": (_I, [_P, _L, _I, _I, _I, _P, _I, _F, _P, _I, _P, _P, _P, _I, _I, _P, _I, _P]),
-    "omc_rotary_q": (_I, [_P, _L, _I, _I, _I, _I, _P, _I, _P, _P, _I, _I, _P]),
+    "omc_rotary_q": (_I, [_P, _I, _L, _I, _I, _I, _I, _P, _I, _P, _P, _I, _I, _P]),
     "omc_latent_attn": (_I, [_P, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P, _P, _P, _F, _P, _P]),
-    "omc_latent_attn_mma": (_I, [_P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _P, _I, _P, _F, _P, _P, _P, _P]),
+    "omc_latent_attn_mma": (_I, [_P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _P, _I, _P, _F, _P, _I, _P, _P, _P]),
+    "omc_latent_decode_items": (_I, [_P, _P, _I, _I, _I, _P, _P, _P]),
     "omc_router_topk": (_I, [_P, _L, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P]),
     "omc_moe_plan_tiles": (_I, [_P, _I, _I, _I, _P, _P, _P, _P]),
     "omc_moe_scatter_rows": (_I, [_P, _I, _L, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P]),
@@ -138,8 +139,8 @@ def latent_kv_store(dkv: torch.Tensor, r: int, dr: int, w: torch.Tensor, eps: fl
 def rotary_q(q32: torch.Tensor, H: int, dn: int, dr: int, cs: torch.Tensor, rot_dims: int, pos: torch.Tensor, qcat: torch.Tensor,
              r: int):
     _need_cuda(q32, cs, pos, qcat)
-    assert q32.dtype == torch.float32 and qcat.is_contiguous() and qcat.shape[-1] == r + dr
-    rc = load().omc_rotary_q(_ptr(q32), q32.stride(0), q32.shape[0], H, dn, dr, _ptr(cs), rot_dims, _ptr(pos), _ptr(qcat),
+    assert qcat.is_contiguous() and qcat.shape[-1] == r + dr and q32.stride(1) == 1
+    rc = load().omc_rotary_q(_ptr(q32), _dt(q32), q32.stride(0), q32.shape[0], H, dn, dr, _ptr(cs), rot_dims, _ptr(pos), _ptr(qcat),
                              _dt(qcat), r, _stream())
     _check(rc, "omc_rotary_q")
 
@@ -172,7 +173,9 @@ class LatentAttnPlan:
     Contexts are cut into key ranges (multiples of 64 keys, at least `min_keys` each) while the step has fewer CTAs than
     `target_ctas`, so that a few decode rows over a long context still fill the device."""
 
-    def __init__(self, portions, H: int, device, target_ctas: int = 296, min_keys: int = 256):
+    MAX_PARTS = 64  # key ranges one merge group may have (csrc/latent_attention.cu: kMergeMaxParts)
+
+    def __init__(self, portions, H: int, device, target_ctas: int = 296, min_keys: int = 128):
         import numpy as np
         tok = max(1, MMA_ROWS // H)
         base = sum(-(-n // tok) for _, n, _, _ in portions)
@@ -183,7 +186,7 @@ class LatentAttnPlan:
             keys = p0 + starts + ntok                                  # keys the tile's last row sees
             parts = np.ones_like(starts)
             if base < target_ctas // 2:
-                parts = np.clip(np.minimum(-(-keys // min_keys), -(-target_ctas // max(base, 1))), 1, None)
+                parts = np.clip(np.minimum(-(-keys // min_keys), -(-target_ctas // max(base, 1))), 1, self.MAX_PARTS)
             for i in range(len(starts)):
                 np_i, k = int(parts[i]), int(keys[i])
                 fr, nt = first_row + int(starts[i]), int(ntok[i])
@@ -204,6 +207,31 @@ class LatentAttnPlan:
         self.merges = buf[self.n_items * 8:] if merges else None
 
 
+class DecodeAttnPlan:
+    """Work list of a decode-only step of B rows with static device buffers: `fill(pos, slot)` rewrites it on the device each step
+    (omc_latent_decode_items), so a captured CUDA graph stays valid while the contexts grow. parts: key ranges per row."""
+
+    def __init__(self, B: int, H: int, parts: int, device):
+        self.B, self.H, self.parts = B, H, parts
+        self.items = torch.zeros(B * parts * 8, device=device, dtype=torch.int32)
+        self.merges = torch.zeros(B * 4, device=device, dtype=torch.int32) if parts > 1 else None
+        self.n_items = B * parts
+        self.n_merges = B if parts > 1 else 0
+        self.n_parts = B * parts if parts > 1 else 0
+
+    @staticmethod
+    def parts_for(B: int, max_keys: int, target_ctas: int = 296, min_keys: int = 128) -> int:
+        """Key ranges per row for contexts up to max_keys (rounded up to a power of two, so that a growing context changes the
+        answer - and with it the captured graph - only a few times)."""
+        bucket = 1 << max(max_keys - 1, 0).bit_length()
+        return max(1, min(bucket // min_keys, -(-target_ctas // B), LatentAttnPlan.MAX_PARTS))
+
+    def fill(self, pos: torch.Tensor, slot: torch.Tensor):
+        rc = load().omc_latent_decode_items(_ptr(pos), _ptr(slot), self.B, self.H, self.parts, _ptr(self.items), _ptr(self.merges),
+                                            _stream())
+        _check(rc, "omc_latent_decode_items")
+
+
 _mma_ws = {}
 
 
@@ -211,7 +239,7 @@ def latent_attn_mma(qcat: torch.Tensor, r: int, dr: int, pool: torch.Tensor, blo
                     plan: LatentAttnPlan, sink: Optional[torch.Tensor], scale: float, out: torch.Tensor):
     _need_cuda(qcat, pool, block_table, plan.items, sink, out)
     T, H = qcat.shape[0], qcat.shape[1]
-    assert qcat.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and out.dtype == torch.float32
+    assert qcat.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16
     assert qcat.is_contiguous() and out.is_contiguous() and pool.is_contiguous()
     ws_o = ws_ml = None
     if plan.n_parts:
@@ -224,7 +252,7 @@ def latent_attn_mma(qcat: torch.Tensor, r: int, dr: int, pool: torch.Tensor, blo
         ws_o, ws_ml = ws[:plan.n_parts * MMA_ROWS * r], ws[plan.n_parts * MMA_ROWS * r:]
     rc = load().omc_latent_attn_mma(_ptr(qcat), T, H, r, dr, _ptr(pool), _ptr(block_table), block_table.shape[1], page_size,
                                     _ptr(plan.items), plan.n_items, _ptr(plan.merges), plan.n_merges, _ptr(sink), scale, _ptr(out),
-                                    _ptr(ws_o), _ptr(ws_ml), _stream())
+                                    _dt(out), _ptr(ws_o), _ptr(ws_ml), _stream())
     _check(rc, "omc_latent_attn_mma")
     if plan.n_merges:
         _core.add_launches(1)

@@ -217,6 +217,8 @@ class StepScheduler:
         self.queue: deque = deque()
         self.results: Dict[int, List[int]] = {}
         self._gen: Dict[str, _GenRequest] = {}
+        self._pinned = None   # host staging of a decode-only step's (tokens, positions, slots)
+        self._pin_event = None
         self._next_id = 0
         self.steps_run = 0
 
@@ -277,10 +279,24 @@ class StepScheduler:
             dev = self.model.device
             self.cache.sync()
             meta = torch.tensor([toks, pos, slot], dtype=torch.int32)
-            if torch.device(dev).type == "cuda":
-                meta = meta.pin_memory().to(dev, non_blocking=True)
-            wr = torch.tensor(want, dtype=torch.int64).to(dev) if want else None
-            logits = self.model.step(meta[0], meta[1], meta[2], self.cache, wr, portions=portions)
+            decode_only = all(n == 1 for _, n, _, _ in portions) and hasattr(self.model, "decode_step")
+            if decode_only and torch.device(dev).type == "cuda":
+                # one token per request: the model's captured decode step (CUDA graph) computes the logits of every row
+                if self._pin_event is not None:
+                    self._pin_event.synchronize()      # the previous step's copy out of the staging buffer has been done
+                if self._pinned is None or self._pinned.shape[1] != len(toks):
+                    self._pinned = torch.empty(3, len(toks), dtype=torch.int32).pin_memory()
+                self._pinned.copy_(meta)
+                logits = self.model.decode_step(self._pinned, self.cache, max(pos) + 1)
+                self._pin_event = torch.cuda.Event()
+                self._pin_event.record()
+                if len(want) != len(toks):
+                    logits = logits[torch.tensor(want, dtype=torch.int64).to(dev)] if want else None
+            else:
+                if torch.device(dev).type == "cuda":
+                    meta = meta.pin_memory().to(dev, non_blocking=True)
+                wr = torch.tensor(want, dtype=torch.int64).to(dev) if want else None
+                logits = self.model.step(meta[0], meta[1], meta[2], self.cache, wr, portions=portions)
             self.steps_run += 1
         for key in end:
             self.release(key)

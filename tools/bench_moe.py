@@ -33,14 +33,15 @@ def main():
         print(json.dumps(rec))
 
 
-def measure(layers=24, batches=(1, 32), ctx=1024, steps=64, prefill=8):
-    """-> list of records (one for the prefill, one per decode batch size); see the module docstring."""
+def measure(layers=24, batches=(1, 32), ctx=1024, steps=64, prefill=8, cfg_kw=None):
+    """-> list of records (one for the prefill, one per decode batch size); see the module docstring.
+    cfg_kw: OmChatQwen2MoeConfig fields that replace the Qwen1.5-MoE-A2.7B sizes (hidden_size must be 128 x heads)."""
     class a:  # noqa: N801
         pass
     a.layers, a.batch, a.ctx, a.steps, a.prefill = layers, list(batches), ctx, steps, prefill
     out = []
     lib.load()
-    cfg = OmChatQwen2MoeConfig(num_hidden_layers=a.layers, mm_vision_tower=None)
+    cfg = OmChatQwen2MoeConfig(num_hidden_layers=a.layers, mm_vision_tower=None, **(cfg_kw or {}))
     w = random_init(cfg, device="cuda:0", vision=False)
     dec = Qwen2MoeDecoder(cfg, w.llm)
     peak_hbm, peak_tf = 6535.4, 1400.0
