@@ -310,6 +310,7 @@ __global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a)
       cp_async_wait_all();
     }
     __syncthreads();
+    if (rg * 16 < n_rows) {  // a row group without rows (decode: H rows of the 64) only helps staging the tiles
     // S = Q K^T for this warp's 16 rows x 64 keys
     float s[8][4];
 #pragma unroll
@@ -386,6 +387,7 @@ __global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a)
         }
       }
     }
+    }
     __syncthreads();  // every warp is done with this tile's buffer
   }
   // row sums over the quad
@@ -432,38 +434,52 @@ __global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a)
   }
 }
 
-// merges[i] = (first q row = first_row * H, n_rows, first part slot, n_parts): blockIdx.y picks 8 of the group's rows, one warp each.
+// merges[i] = (first q row = first_row * H, n_rows, first part slot, n_parts): one CTA per (group, row), threads over columns,
+// four parts' loads in flight per thread (a warp that walked parts and columns one load at a time spent 70 us on latency).
 constexpr int kMergeMaxParts = 64;
 template <typename TO>
-__global__ void __launch_bounds__(256) latent_attn_merge_kernel(const int32_t* __restrict__ merges, const float* __restrict__ ws_o,
+__global__ void __launch_bounds__(128) latent_attn_merge_kernel(const int32_t* __restrict__ merges, const float* __restrict__ ws_o,
                                                                 const float* __restrict__ ws_ml, const float* __restrict__ sink, int H,
                                                                 int r, TO* __restrict__ out) {
-  __shared__ float s_f[8][kMergeMaxParts];
+  __shared__ float s_f[kMergeMaxParts];
+  __shared__ float s_inv;
   const int32_t* mg = merges + blockIdx.x * 4;
   const int qrow0 = mg[0], n_rows = mg[1], part0 = mg[2], n_parts = mg[3];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = blockIdx.y * 8 + warp;
+  const int row = blockIdx.y;
   if (row >= n_rows) return;
-  // factors exp2(m_p - m) / denominator of every part, computed once per row
-  float mt = -INFINITY;
-  for (int p = lane; p < n_parts; p += 32) mt = fmaxf(mt, ws_ml[((long long)(part0 + p) * kMmaRows + row) * 2]);
-  mt = seq_warp_max(mt);
-  const float sk = sink != nullptr ? sink[(qrow0 + row) % H] * 1.4426950408889634f : -INFINITY;
-  mt = fmaxf(mt, sk);
-  float den = 0.f;
-  for (int p = lane; p < n_parts; p += 32) {
-    const float* ml = ws_ml + ((long long)(part0 + p) * kMmaRows + row) * 2;
-    const float f = ml[0] == -INFINITY ? 0.f : exp2f(ml[0] - mt);
-    s_f[warp][p] = f;
-    den += ml[1] * f;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float mt = -INFINITY;
+    for (int p = lane; p < n_parts; p += 32) mt = fmaxf(mt, ws_ml[((long long)(part0 + p) * kMmaRows + row) * 2]);
+    mt = seq_warp_max(mt);
+    const float sk = sink != nullptr ? sink[(qrow0 + row) % H] * 1.4426950408889634f : -INFINITY;
+    mt = fmaxf(mt, sk);
+    float den = 0.f;
+    for (int p = lane; p < n_parts; p += 32) {
+      const float* ml = ws_ml + ((long long)(part0 + p) * kMmaRows + row) * 2;
+      const float f = ml[0] == -INFINITY ? 0.f : exp2f(ml[0] - mt);
+      s_f[p] = f;
+      den += ml[1] * f;
+    }
+    den = seq_warp_sum(den);
+    if (sink != nullptr) den += exp2f(sk - mt);
+    if (lane == 0) s_inv = 1.f / den;
   }
-  den = seq_warp_sum(den);
-  if (sink != nullptr) den += exp2f(sk - mt);
-  const float inv = 1.f / den;
-  __syncwarp();
-  for (int c = lane; c < r; c += 32) {
+  __syncthreads();
+  const float inv = s_inv;
+  const float* base = ws_o + ((long long)part0 * kMmaRows + row) * r;
+  const long long ps = (long long)kMmaRows * r;  // stride between parts
+  for (int c = threadIdx.x; c < r; c += blockDim.x) {
     float v = 0.f;
-    for (int p = 0; p < n_parts; ++p) v = fmaf(ws_o[((long long)(part0 + p) * kMmaRows + row) * r + c], s_f[warp][p], v);
+    int p = 0;
+    for (; p + 4 <= n_parts; p += 4) {
+      const float a0 = base[p * ps + c], a1 = base[(p + 1) * ps + c], a2 = base[(p + 2) * ps + c], a3 = base[(p + 3) * ps + c];
+      v = fmaf(a0, s_f[p], v);
+      v = fmaf(a1, s_f[p + 1], v);
+      v = fmaf(a2, s_f[p + 2], v);
+      v = fmaf(a3, s_f[p + 3], v);
+    }
+    for (; p < n_parts; ++p) v = fmaf(base[p * ps + c], s_f[p], v);
     stf(out + ((long long)qrow0 + row) * r + c, v * inv);
   }
 }
@@ -546,9 +562,9 @@ extern "C" int omc_latent_attn_mma(const void* qcat, int T, int H, int r, int dr
   else rc = launch_lat_mma<2, 32>(a, out_dt, n_items, smem, st);
   if (rc != OMC_OK || n_merges == 0) return rc;
   if (out_dt == OMC_DT_BF16)
-    latent_attn_merge_kernel<bf16_t><<<dim3(n_merges, kMmaRows / 8), 256, 0, st>>>(merges, ws_o, ws_ml, sink, H, r, static_cast<bf16_t*>(out));
+    latent_attn_merge_kernel<bf16_t><<<dim3(n_merges, kMmaRows), 128, 0, st>>>(merges, ws_o, ws_ml, sink, H, r, static_cast<bf16_t*>(out));
   else
-    latent_attn_merge_kernel<float><<<dim3(n_merges, kMmaRows / 8), 256, 0, st>>>(merges, ws_o, ws_ml, sink, H, r, static_cast<float*>(out));
+    latent_attn_merge_kernel<float><<<dim3(n_merges, kMmaRows), 128, 0, st>>>(merges, ws_o, ws_ml, sink, H, r, static_cast<float*>(out));
   return check_launch("omc_latent_attn_merge");
 }
 

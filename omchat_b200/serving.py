@@ -78,6 +78,11 @@ class ContinuousBatcher:
         self._next_id = 0
         self.steps_run = 0
 
+    @property
+    def free_pages(self) -> List[int]:
+        """Page ids currently free (the allocator's list, most recently freed last)."""
+        return self.pages._free
+
     # ------------------------------------------------------------------------------------------------ public
     def submit(self, input_ids: torch.Tensor, images: Optional[torch.Tensor] = None, max_new_tokens: int = 64,
                eos_token_id: Optional[int] = None) -> int:
