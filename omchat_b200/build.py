@@ -1,11 +1,13 @@
 """In-tree build of the C-ABI CUDA libraries (sm_100a).
 
-Two libraries, so that a process compiles only what its model needs:
+Separate libraries, so that a process compiles only what its model needs:
   core  omchat_b200/_lib/libomchat_b200.so      tcgen05 GEMMs, flash attention, the persistent decode kernel, the vision tower's
                                                 row kernels, preprocessing (include/omchat_b200.h)
   seq   omchat_b200/_lib/libomchat_b200_seq.so  sequence-step kernels: latent attention over a paged cache, fp32 residual row
                                                 kernels, the score-corrected router, the any-shape linear layer
                                                 (include/omchat_b200_seq.h); built with IEEE division / square root / exp
+  dense omchat_b200/_lib/libomchat_b200_dense.so  the GEMM / row-kernel / sampling subset of core, for a process that has no core
+                                                library (lib.load_dense() prefers a built core library, which has the same symbols)
 `python -m omchat_b200.build [core|seq ...]` or `__graft_entry__.build()` builds both; nvcc cross-compiles without a GPU. The
 libraries are git-ignored but travel to the GPU box with the repo snapshot. `ensure(name)` builds one library on demand (first
 use in a fresh checkout).
@@ -26,12 +28,17 @@ LIB = LIBDIR / "libomchat_b200.so"
 SEQ_LIB = LIBDIR / "libomchat_b200_seq.so"
 SOURCES = ["capi.cu", "gemm_sm100.cu", "gemm_skinny.cu", "gemm_stream.cu", "gemv.cu", "rowops.cu", "attention.cu", "attention_sm100.cu", "decode_mega.cu", "preprocess.cu", "model_capi.cu", "moe.cu"]
 SEQ_SOURCES = ["capi.cu", "linear_any.cu", "rownorm32.cu", "latent_attention.cu", "router_moe.cu"]
+DENSE_LIB = LIBDIR / "libomchat_b200_dense.so"
+DENSE_SOURCES = ["capi.cu", "gemm_sm100.cu", "gemm_skinny.cu", "rowops.cu", "moe.cu"]  # a subset of SOURCES that links on its own
 BASE_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 NVCC_FLAGS = BASE_FLAGS + ["--use_fast_math"]
 NVCC_FLAGS += os.environ.get("OMCHAT_B200_NVCC_EXTRA", "").split()  # e.g. -DOMC_MEGA_DETAIL=1 for tools/prof_mega.py
 COMPONENTS = {
     "core": (LIB, SOURCES, NVCC_FLAGS),
     "seq": (SEQ_LIB, SEQ_SOURCES, BASE_FLAGS),  # no fast-math: its fp32 mode is true fp32
+    # the core library's GEMMs (tcgen05, skinny, grouped), row kernels and sampling alone: what a sequence-step model needs of it
+    # when a layer is wide enough for the tensor-core GEMMs and no full core library has been built
+    "dense": (DENSE_LIB, DENSE_SOURCES, NVCC_FLAGS),
 }
 
 
@@ -95,7 +102,7 @@ def ensure(name: str) -> Path:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Builds every library; returns the core library's path."""
+    """Builds the seq and the core library (the dense subset is built on demand only); returns the core library's path."""
     build_component("seq", force, verbose)
     return build_component("core", force, verbose)
 

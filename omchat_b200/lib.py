@@ -115,6 +115,31 @@ def load() -> ctypes.CDLL:
     return lib
 
 
+_dense = None
+
+
+def load_dense() -> ctypes.CDLL:
+    """The library that holds the GEMMs (tcgen05, skinny, grouped), the row kernels and omc_argmax: the full core library when it
+    is loaded or has been built; else its `dense` subset, compiled on first use (build.ensure("dense")). Models that need nothing
+    else of the core library (model/voduzen.py) call their GEMMs and the sampler through this."""
+    global _dense
+    if _lib is not None:
+        return _lib
+    if _dense is not None:
+        return _dense
+    if os.environ.get("OMCHAT_B200_LIB") or LIB_PATH.exists():
+        return load()
+    from . import build
+    lib = ctypes.CDLL(str(build.ensure("dense")))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name, None)
+        if fn is not None:
+            fn.restype = res
+            fn.argtypes = args
+    _dense = lib
+    return lib
+
+
 _KERNELS_PER_CALL = {"omc_splice": 2, "omc_argmax": 2}
 
 
@@ -122,7 +147,7 @@ def _check(rc: int, what: str):
     global _launches
     _launches += _KERNELS_PER_CALL.get(what, 1)
     if rc != 0:
-        msg = load().omc_last_error().decode(errors="replace")
+        msg = load_dense().omc_last_error().decode(errors="replace")
         raise OmcError(f"{what} failed ({rc}): {msg}")
 
 
@@ -159,7 +184,7 @@ def _skinny_workspace(device, n: int) -> torch.Tensor:
     """Zeroed split-K workspace of the skinny GEMM, one per device, grown on demand (the kernel leaves it zeroed)."""
     key = str(device)
     ws = _skinny_ws.get(key)
-    need = load().omc_gemm_skinny_workspace_bytes(max(n, 160 * 1024))
+    need = load_dense().omc_gemm_skinny_workspace_bytes(max(n, 160 * 1024))
     if ws is None or ws.numel() < need:
         ws = torch.zeros(need, device=device, dtype=torch.uint8)
         _skinny_ws[key] = ws
@@ -200,7 +225,7 @@ def _gemm_autotune(x, w, out, bias, scale, res, epi, out_f32) -> int:
             _l2_flush.zero_()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            rc = load().omc_gemm_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(scratch), scratch.stride(0), M, N, K,
+            rc = load_dense().omc_gemm_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(scratch), scratch.stride(0), M, N, K,
                                       _ptr(bias), _ptr(scale), _ptr(res), res.stride(0) if res is not None else 0, epi,
                                       1 if out_f32 else 0, c, _stream())
             e1.record()
@@ -267,7 +292,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
         if ssq_out is not None:
             assert ssq_out.rows >= M
             nf.ssq_out, nf.ssq_out_ld, nf.ssq_out_max_parts = ssq_out.buf.data_ptr(), ssq_out.rows, RowSsq.MAX_PARTS
-        rc = load().omc_gemm_bf16_norm(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K,
+        rc = load_dense().omc_gemm_bf16_norm(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K,
                                        _ptr(bias), _ptr(scale), _ptr(res), res.stride(0) if res is not None else 0, epi,
                                        1 if out_f32 else 0, tile_cfg, ctypes.byref(nf), _stream())
         _check(rc, "omc_gemm_bf16_norm")
@@ -276,14 +301,14 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
         return out
     if M <= SKINNY_MAX_M and tile_cfg == 0 and SKINNY_ENABLED:
         ws = _skinny_workspace(x.device, N)
-        rc = load().omc_gemm_skinny_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K,
+        rc = load_dense().omc_gemm_skinny_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K,
                                          _ptr(bias), _ptr(scale), _ptr(res), res.stride(0) if res is not None else 0, epi,
                                          1 if out_f32 else 0, ws.data_ptr(), ws.numel(), _stream())
         _check(rc, "omc_gemm_skinny_bf16")
         return out
     if tile_cfg == 0 and GEMM_AUTOTUNE and M <= GEMM_AUTOTUNE_MAX_M:
         tile_cfg = _gemm_autotune(x, w, out, bias, scale, res, epi, out_f32)
-    rc = load().omc_gemm_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K,
+    rc = load_dense().omc_gemm_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K,
                               _ptr(bias), _ptr(scale), _ptr(res), res.stride(0) if res is not None else 0, epi,
                               1 if out_f32 else 0, tile_cfg, _stream())
     _check(rc, "omc_gemm_bf16")
@@ -297,7 +322,7 @@ def gemm_grouped(x: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, ou
     _need_cuda(x, w, tile_expert, out)
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.dim() == 3 and w.is_contiguous() and x.stride(1) == 1
     E, N, K = w.shape
-    fn = load().omc_gemm_bf16_grouped_f32 if out.dtype == torch.float32 else load().omc_gemm_bf16_grouped
+    fn = load_dense().omc_gemm_bf16_grouped_f32 if out.dtype == torch.float32 else load_dense().omc_gemm_bf16_grouped
     rc = fn(_ptr(x), x.stride(0), x.shape[0], _ptr(w), K, E, N, K, _ptr(tile_expert), active_tiles_hint, _ptr(out), out.stride(0),
             epi, _stream())
     _check(rc, "omc_gemm_bf16_grouped")
@@ -589,7 +614,7 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, workspace: 
         out = torch.empty(B, device=logits.device, dtype=torch.int64)
     if workspace is None:
         workspace = torch.empty(128 * B, device=logits.device, dtype=torch.float32)
-    rc = load().omc_argmax(_ptr(logits), logits.stride(0), B, V, _ptr(out), _ptr(workspace), _stream())
+    rc = load_dense().omc_argmax(_ptr(logits), logits.stride(0), B, V, _ptr(out), _ptr(workspace), _stream())
     _check(rc, "omc_argmax")
     return out
 
