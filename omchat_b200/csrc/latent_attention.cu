@@ -195,9 +195,10 @@ extern "C" int omc_latent_attn(const void* qcat, int q_dt, int T, int H, int r, 
 // Tensor-core kernel (bf16 storage). Rows of a tile are (token, head) pairs of one sequence portion - 64 consecutive rows of
 // qcat viewed as [T * H, r + dr] - so that all heads of a token share the key tile that is staged for them; a 64-key tile
 // [64][r + dr] in shared memory is the B operand of S = Q K^T as it lies (ldmatrix) and, through ldmatrix.trans over its first
-// r columns, the B operand of O += P V: the cache row is read once for both. 4 row groups of 16 rows x VS value splits = 4 * VS
-// warps; with VS = 2 both warps of a row group compute the same scores and each keeps half of the output columns in registers
-// (r = 512 would need 256 accumulator registers per thread otherwise). Long contexts of decode rows are cut into key ranges that
+// r columns, the B operand of O += P V: the cache row is read once for both. 4 row groups of 16 rows x VS warps each = 4 * VS
+// warps: the VS warps of a row group split the tile's keys for the scores (row maxima and the bf16 probabilities are exchanged
+// through shared memory) and the r output columns for P V (r = 512 in one warp would need 256 accumulator registers per thread;
+// with VS = 4 a CTA has 16 warps to hide the latency of the dependent mma chains). Long contexts of decode rows are cut into key ranges that
 // different CTAs take; their (max, sum, unnormalised output) partials are merged by latent_attn_merge_kernel, which also adds
 // the sink term to the denominator.
 namespace omc {
@@ -224,6 +225,12 @@ __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
 }
 
 constexpr int kMmaRows = 64, kMmaKeys = 64;
+constexpr int kPPitch = kMmaKeys + 8;  // row pitch of the probability tile the two warps of a row group exchange
+constexpr int kMaxVS = 4;               // warps that share a row group (value columns and keys of a tile are split between them)
+constexpr int kPairBytes = kMmaRows * kPPitch * 2 + kMaxVS * kMmaRows * 4;
+// barrier of the VS warps (rg, rg + 4, ...) that share a row group
+template <int VS>
+__device__ __forceinline__ void group_sync(int rg) { asm volatile("bar.sync %0, %1;" ::"r"(rg + 1), "n"(32 * VS) : "memory"); }
 
 struct LatMmaArgs {
   const bf16_t* q;
@@ -294,6 +301,10 @@ __global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a)
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   bf16_t* Kbuf[2] = {Ks, a.two_buffers ? Ks + kMmaKeys * pitch : Ks};
+  constexpr int NS = 8 / VS;                 // 8-key score tiles per warp
+  const int kofs = vs * (kMmaKeys / VS);     // first key of this warp's share of a tile
+  bf16_t* Ps = Ks + (a.two_buffers ? 2 : 1) * kMmaKeys * pitch;       // [64][kPPitch] probabilities (VS > 1 only)
+  float* s_x = reinterpret_cast<float*>(Ps + kMmaRows * kPPitch);     // [VS][64] row maxima / sums of the warps of a row group
   if (kb < k_end) stage_keys(Kbuf[0], kb);
   int kt = 0;
   for (int j0 = kb; j0 < k_end; j0 += kMmaKeys, ++kt) {
@@ -311,28 +322,44 @@ __global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a)
     }
     __syncthreads();
     if (rg * 16 < n_rows) {  // a row group without rows (decode: H rows of the 64) only helps staging the tiles
-    // S = Q K^T for this warp's 16 rows x 64 keys
-    float s[8][4];
+    // S = Q K^T for this warp's 16 rows x its keys: all 64 keys, or with two warps per row group the half [vs * 32, vs * 32 + 32)
+    // (the partner computes the other half; the row maximum and the probabilities are exchanged through shared memory)
+    float s[NS][4], s2[NS][4];  // two accumulator sets over alternating K slices: twice the independent mma chains per warp
 #pragma unroll
-    for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    for (int n = 0; n < NS; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = s2[n][0] = s2[n][1] = s2[n][2] = s2[n][3] = 0.f;
     const uint32_t q_base = smem_u32(Qs + (rg * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * pitch + 8 * (lane >> 4));
-    const uint32_t k_base = smem_u32(Kc + ((lane & 7) + 8 * (lane >> 4)) * pitch + 8 * ((lane >> 3) & 1));
-    for (int kk = 0; kk < D; kk += 16) {
-      uint32_t a0, a1, a2, a3;
+    const uint32_t k_base = smem_u32(Kc + (kofs + (lane & 7) + 8 * (lane >> 4)) * pitch + 8 * ((lane >> 3) & 1));
+#pragma unroll 2
+    for (int kk = 0; kk < D; kk += 32) {
+      uint32_t a0, a1, a2, a3, c0, c1, c2, c3;
       ldsm_x4(q_base + kk * 2, a0, a1, a2, a3);
+      const bool second = kk + 16 < D;  // D is a multiple of 16, not always of 32
+      if (second) ldsm_x4(q_base + (kk + 16) * 2, c0, c1, c2, c3);
 #pragma unroll
-      for (int n2 = 0; n2 < 4; ++n2) {  // key blocks of 16
+      for (int n2 = 0; n2 < NS / 2; ++n2) {  // key blocks of 16
         uint32_t b0, b1, b2, b3;
         ldsm_x4(k_base + (n2 * 16 * pitch + kk) * 2, b0, b1, b2, b3);
         mma_bf16(s[2 * n2], a0, a1, a2, a3, b0, b1);
         mma_bf16(s[2 * n2 + 1], a0, a1, a2, a3, b2, b3);
+        if (second) {
+          ldsm_x4(k_base + (n2 * 16 * pitch + kk + 16) * 2, b0, b1, b2, b3);
+          mma_bf16(s2[2 * n2], c0, c1, c2, c3, b0, b1);
+          mma_bf16(s2[2 * n2 + 1], c0, c1, c2, c3, b2, b3);
+        }
       }
+    }
+#pragma unroll
+    for (int n = 0; n < NS; ++n) {
+      s[n][0] += s2[n][0];
+      s[n][1] += s2[n][1];
+      s[n][2] += s2[n][2];
+      s[n][3] += s2[n][3];
     }
     // mask + online softmax (base-2 exponent, scale folded in)
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
-      const int key = j0 + n * 8 + 2 * t4;
+    for (int n = 0; n < NS; ++n) {
+      const int key = j0 + kofs + n * 8 + 2 * t4;
       s[n][0] = key <= lim0 ? s[n][0] * a.scale_log2 : -INFINITY;
       s[n][1] = key + 1 <= lim0 ? s[n][1] * a.scale_log2 : -INFINITY;
       s[n][2] = key <= lim1 ? s[n][2] * a.scale_log2 : -INFINITY;
@@ -344,15 +371,27 @@ __global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a)
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    if constexpr (VS > 1) {
+      if (t4 == 0) {
+        s_x[vs * kMmaRows + row0] = mx0;
+        s_x[vs * kMmaRows + row1] = mx1;
+      }
+      group_sync<VS>(rg);
+#pragma unroll
+      for (int v = 0; v < VS; ++v) {
+        mx0 = fmaxf(mx0, s_x[v * kMmaRows + row0]);
+        mx1 = fmaxf(mx1, s_x[v * kMmaRows + row1]);
+      }
+    }
     const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
     const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;  // rows that see nothing yet
     const float c0 = exp2f(m0 - ms0), c1 = exp2f(m1 - ms1);
     m0 = mn0;
     m1 = mn1;
     float rs0 = 0.f, rs1 = 0.f;
-    uint32_t p[8][2];
+    uint32_t p[NS][2];
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
+    for (int n = 0; n < NS; ++n) {
       const float e0 = exp2f(s[n][0] - ms0), e1 = exp2f(s[n][1] - ms0), e2 = exp2f(s[n][2] - ms1), e3 = exp2f(s[n][3] - ms1);
       p[n][0] = pack2_bf16(e0, e1);
       p[n][1] = pack2_bf16(e2, e3);
@@ -362,7 +401,7 @@ __global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a)
       rs0 += f0.x + f0.y;
       rs1 += f1.x + f1.y;
     }
-    l0 = l0 * c0 + rs0;
+    l0 = l0 * c0 + rs0;  // with two warps per row group: the sum over this warp's keys only, completed after the last tile
     l1 = l1 * c1 + rs1;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
@@ -371,11 +410,25 @@ __global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a)
       o[j][2] *= c1;
       o[j][3] *= c1;
     }
+    if constexpr (VS > 1) {
+#pragma unroll
+      for (int n = 0; n < NS; ++n) {
+        *reinterpret_cast<uint32_t*>(Ps + row0 * kPPitch + kofs + n * 8 + 2 * t4) = p[n][0];
+        *reinterpret_cast<uint32_t*>(Ps + row1 * kPPitch + kofs + n * 8 + 2 * t4) = p[n][1];
+      }
+      group_sync<VS>(rg);
+    }
     // O += P V over this warp's output tiles (pairs of 8-column tiles per ldmatrix.x4.trans)
     const uint32_t v_base = smem_u32(Kc + ((lane & 7) + 8 * ((lane >> 3) & 1)) * pitch + 8 * (lane >> 4));
+    const uint32_t p_base = smem_u32(Ps + (rg * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * kPPitch + 8 * (lane >> 4));
 #pragma unroll
     for (int kb16 = 0; kb16 < 4; ++kb16) {
-      const uint32_t a0 = p[2 * kb16][0], a1 = p[2 * kb16][1], a2 = p[2 * kb16 + 1][0], a3 = p[2 * kb16 + 1][1];
+      uint32_t a0, a1, a2, a3;
+      if constexpr (VS > 1) {
+        ldsm_x4(p_base + kb16 * 16 * 2, a0, a1, a2, a3);
+      } else {
+        a0 = p[(2 * kb16) % NS][0], a1 = p[(2 * kb16) % NS][1], a2 = p[(2 * kb16 + 1) % NS][0], a3 = p[(2 * kb16 + 1) % NS][1];
+      }
 #pragma unroll
       for (int j = 0; j < NV; j += 2) {
         const int tile = nv0 + j;
@@ -395,6 +448,20 @@ __global__ void __launch_bounds__(128 * VS) latent_attn_mma_kernel(LatMmaArgs a)
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if constexpr (VS > 1) {  // the other warps' shares of the denominator
+    __syncthreads();
+    if (t4 == 0) {
+      s_x[vs * kMmaRows + row0] = l0;
+      s_x[vs * kMmaRows + row1] = l1;
+    }
+    __syncthreads();
+    l0 = l1 = 0.f;
+#pragma unroll
+    for (int v = 0; v < VS; ++v) {
+      l0 += s_x[v * kMmaRows + row0];
+      l1 += s_x[v * kMmaRows + row1];
+    }
+  }
   if (part < 0) {
     float d0 = l0, d1 = l1;
     if (a.sink != nullptr) {
@@ -544,11 +611,12 @@ extern "C" int omc_latent_attn_mma(const void* qcat, int T, int H, int r, int dr
     return set_error(OMC_ERR_SHAPE, "omc_latent_attn_mma: latent width a multiple of 16 up to 512, rotated width a multiple of 16, at most 64 heads");
   if (n_items == 0) return OMC_OK;
   const int D = r + dr;
-  size_t smem = (size_t)(kMmaRows + 2 * kMmaKeys) * (D + 8) * sizeof(bf16_t);
+  const size_t extra = r > 128 ? kPairBytes : 0;  // several warps per row group exchange probabilities
+  size_t smem = (size_t)(kMmaRows + 2 * kMmaKeys) * (D + 8) * sizeof(bf16_t) + extra;
   int two = 1;
   if (smem > 227 * 1024) {
     two = 0;
-    smem = (size_t)(kMmaRows + kMmaKeys) * (D + 8) * sizeof(bf16_t);
+    smem = (size_t)(kMmaRows + kMmaKeys) * (D + 8) * sizeof(bf16_t) + extra;
   }
   if (smem > 227 * 1024) return set_error(OMC_ERR_SHAPE, "omc_latent_attn_mma: rows too wide for shared memory");
   LatMmaArgs a{static_cast<const bf16_t*>(qcat), static_cast<const bf16_t*>(pool), block_table, items, sink, out, ws_o, ws_ml,
@@ -559,7 +627,7 @@ extern "C" int omc_latent_attn_mma(const void* qcat, int T, int H, int r, int dr
   if (r <= 64) rc = launch_lat_mma<1, 8>(a, out_dt, n_items, smem, st);
   else if (r <= 128) rc = launch_lat_mma<1, 16>(a, out_dt, n_items, smem, st);
   else if (r <= 256) rc = launch_lat_mma<2, 16>(a, out_dt, n_items, smem, st);
-  else rc = launch_lat_mma<2, 32>(a, out_dt, n_items, smem, st);
+  else rc = launch_lat_mma<4, 16>(a, out_dt, n_items, smem, st);  // 16 warps: four per row group, 128 value columns and 16 keys each
   if (rc != OMC_OK || n_merges == 0) return rc;
   if (out_dt == OMC_DT_BF16)
     latent_attn_merge_kernel<bf16_t><<<dim3(n_merges, kMmaRows), 128, 0, st>>>(merges, ws_o, ws_ml, sink, H, r, static_cast<bf16_t*>(out));

@@ -349,7 +349,7 @@ def run_attn(impl, q, r, dr, pool, table, page, pos, slot, sink, scale):
     return out.cpu()
 
 
-KERNELS = [("plain", 16, 8), ("plain", 32, 16), ("mma", 32, 16), ("mma", 144, 16)]
+KERNELS = [("plain", 16, 8), ("plain", 32, 16), ("mma", 32, 16), ("mma", 144, 16), ("mma", 288, 32)]  # mma: 1, 2 and 4 warps per row group
 
 
 def attn_case(page, n, qpos, hot, decode, impl="plain", r=16, dr=8):
