@@ -89,6 +89,9 @@ constexpr int kMmaBM = 128, kMmaBN = 128, kMmaBK = 32, kMmaPitch = kMmaBK + 8;
 
 __device__ __forceinline__ uint32_t lin_smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
+__device__ __forceinline__ void store_pair(float* p, float x, float y) { *reinterpret_cast<float2*>(p) = make_float2(x, y); }
+__device__ __forceinline__ void store_pair(bf16_t* p, float x, float y) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(x, y); }
+
 template <typename TY>
 __global__ void __launch_bounds__(256) linear_mma_kernel(LinearArgs a) {
   __shared__ __align__(16) bf16_t As[2][kMmaBM * kMmaPitch];
@@ -153,15 +156,25 @@ __global__ void __launch_bounds__(256) linear_mma_kernel(LinearArgs a) {
     __syncthreads();
   }
   const int g = lane >> 2, t4 = lane & 3;
+  // an accumulator pair (columns n, n + 1) goes out as one 4- or 8-byte store when the row is laid out for it
+  const bool pair_ok = (a.ldy % 2 == 0) && (a.sy % 2 == 0) && (reinterpret_cast<uintptr_t>(a.Y) % (2 * sizeof(TY)) == 0);
 #pragma unroll
   for (int mm = 0; mm < 4; ++mm)
 #pragma unroll
     for (int nn = 0; nn < 4; ++nn)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int m = m0 + wm * 64 + mm * 16 + g + 8 * (e >> 1);
-        const int n = n0 + wn * 32 + nn * 8 + 2 * t4 + (e & 1);
-        if (m < a.M && n < a.N) stf(Y + (long long)m * a.ldy + n, apply_act(acc[mm][nn][e] * a.alpha, a.act));
+      for (int hh = 0; hh < 2; ++hh) {
+        const int m = m0 + wm * 64 + mm * 16 + g + 8 * hh;
+        const int n = n0 + wn * 32 + nn * 8 + 2 * t4;
+        if (m >= a.M || n >= a.N) continue;
+        const float v0 = apply_act(acc[mm][nn][2 * hh] * a.alpha, a.act), v1 = apply_act(acc[mm][nn][2 * hh + 1] * a.alpha, a.act);
+        TY* dst = Y + (long long)m * a.ldy + n;
+        if (pair_ok && n + 1 < a.N) {
+          store_pair(dst, v0, v1);
+        } else {
+          stf(dst, v0);
+          if (n + 1 < a.N) stf(dst + 1, v1);
+        }
       }
 }
 

@@ -199,6 +199,8 @@ class VoduzenDecoder:
             f, mult = spec.rot.frequencies()
             ang = torch.arange(n, dtype=torch.float64)[:, None] * torch.tensor(f, dtype=torch.float64)[None, :]
             t = (torch.stack([ang.cos(), ang.sin()], dim=-1) * mult).to(torch.float32).contiguous().to(self.device)
+            if t.numel() == 0:   # no rotated dimensions: the kernels still want a valid pointer
+                t = torch.zeros(n, 1, 2, device=self.device)
             mw.rot_cs = t
         return t
 

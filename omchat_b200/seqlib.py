@@ -163,8 +163,9 @@ MMA_ROWS = 64  # rows ((token, head) pairs) and keys per tile of the tensor-core
 
 def latent_attn_mma_ok(H: int, r: int, dr: int, dtype: torch.dtype) -> bool:
     """Shapes the tensor-core kernel takes; everything else runs on the plain kernel."""
+    exchange = (MMA_ROWS * (MMA_ROWS + 8) * 2 + 4 * MMA_ROWS * 4) if r > 128 else 0   # probabilities / row statistics of a row group
     return (dtype == torch.bfloat16 and H <= MMA_ROWS and r % 16 == 0 and 0 < r <= 512 and dr % 16 == 0
-            and 2 * MMA_ROWS * (r + dr + 8) * 2 <= 227 * 1024)
+            and 2 * MMA_ROWS * (r + dr + 8) * 2 + exchange <= 227 * 1024)
 
 
 class LatentAttnPlan:
