@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(LinearArgs a) {
   }
 }
 
-// ---- bf16 x bf16 on the tensor pipe (mma.sync.m16n8k16): the same contract for operands whose rows start on 16-byte boundaries.
+// ---- bf16 x bf16 on the tensor pipe (mma.sync.m16n8k16): the same interface for operands whose rows start on 16-byte boundaries.
 // 128 x 128 output tile, K slices of 32 double-buffered with cp.async, 8 warps of 64 x 32. It serves the batched per-head products
 // of latent attention (absorbing W_uk into the query, W_uv after the attention), whose heads are column slices of one buffer.
 constexpr int kMmaBM = 128, kMmaBN = 128, kMmaBK = 32, kMmaPitch = kMmaBK + 8;
