@@ -319,6 +319,22 @@ def test_long_decoding_in_fp32():
     assert rel_err(got["a"], O.forward(cfg, sd, toks)) < 2e-4
 
 
+def test_long_decoding_in_bf16_through_growing_key_ranges():
+    """Decode-only steps replay a CUDA graph whose attention work list is rebuilt on the device; as the context passes 128, 256
+    and 512 tokens the rows are cut into 1, 2, 4 and 8 key ranges (new graphs) that the merge kernel combines."""
+    cfg = config_c(page=16)
+    model, sd = build(cfg, torch.bfloat16, seed=15)
+    toks = tokens(560, cfg["vocab"], 33)
+    got, _ = run_schedule(model, [[("a", toks[:100])]] + [[("a", [t])] for t in toks[100:]], max_tokens=576)
+    assert len(model.decoder._graphs) >= 3
+    assert close(got["a"], O.forward(cfg, sd, toks), torch.bfloat16)
+    # two requests decoding side by side at different lengths, against each alone
+    a, b = tokens(300, cfg["vocab"], 34), tokens(140, cfg["vocab"], 35)
+    sch = [[("a", a[:270]), ("b", b[:110])]] + [[("a", [a[270 + i]]), ("b", [b[110 + i]])] for i in range(30)]
+    got, _ = run_schedule(model, sch, max_tokens=512)
+    assert close(got["a"], O.forward(cfg, sd, a), torch.bfloat16) and close(got["b"], O.forward(cfg, sd, b), torch.bfloat16)
+
+
 # ------------------------------------------------------------------------------------------------- engineered cases
 def one_layer(page, sink_value=None):
     l = layer("latent_attention", 2, 8, 8, 8, 16, mlp=None)
