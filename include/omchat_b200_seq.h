@@ -60,6 +60,11 @@ int omc_latent_kv_store(const float* dkv, long long ld, int T, int r, int dr, co
                         int rot_dims, const int32_t* pos, const int32_t* slot, const int32_t* block_table, int max_pages,
                         int page_size, void* pool, int pool_dt, void* stream);
 
+/* omc_latent_kv_store and omc_rotary_q in one launch; w, pool, q and qcat share the dtype dt. */
+int omc_latent_rope_store(const float* dkv, long long ld, int T, int r, int dr, const void* w, float eps, const float* cs, int rot_dims,
+                          const int32_t* pos, const int32_t* slot, const int32_t* block_table, int max_pages, int page_size, void* pool,
+                          const void* q, long long ldq, int H, int dn, void* qcat, int dt, void* stream);
+
 /* Rotated query parts: q [T, H * (dn + dr)] of in_dt (per head dn unrotated then dr rotated dims) -> qcat[t][h][r + j] for
  * j < dr (qcat is [T, H, r + dr] of q_dt; its first r columns per head are written by the absorbing omc_linear). */
 int omc_rotary_q(const void* q, int in_dt, long long ldq, int T, int H, int dn, int dr, const float* cs, int rot_dims,
@@ -107,6 +112,11 @@ int omc_moe_plan_tiles(int32_t* counts, int experts, int tile, int max_tiles, in
                        int32_t* tile_group, void* stream);
 int omc_moe_scatter_rows(const void* x, int dt, long long ldx, int T, int C, const int32_t* ids, int top, int experts,
                          const int32_t* seg_start, int32_t* cursor, int32_t* slot_of, void* xs, long long ldxs, void* stream);
+
+/* omc_moe_plan_tiles + omc_moe_scatter_rows as ONE single-CTA launch, for steps of a few rows (decode). */
+int omc_moe_plan_scatter_small(int32_t* counts, int experts, int tile, int max_tiles, int32_t* seg_start, int32_t* tile_group,
+                               const void* x, int dt, long long ldx, int T, int C, const int32_t* ids, int top, int32_t* slot_of, void* xs,
+                               long long ldxs, void* stream);
 
 /* Combine + output-side norm + residual in one pass over the row:
  * y = sum_j w[t,j] * (slot_of[t,j] >= 0 ? ys[slot_of[t,j]] : h32[t]) + gate[t] * ysh[t]   (ysh / gate may be NULL)

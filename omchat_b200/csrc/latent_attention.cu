@@ -63,6 +63,51 @@ __global__ void __launch_bounds__(128) rotary_q_kernel(const TI* __restrict__ q3
   }
 }
 
+// Both of the above for one row in one launch (a step's decode rows pay per launch, not per byte): the cache append of the row's
+// latent and rotated key part, then the rotated query parts of all heads. All stored operands share one type.
+template <typename T>
+__global__ void __launch_bounds__(128) latent_rope_store_kernel(const float* __restrict__ dkv, long long ld, int r, int dr,
+                                                                const T* __restrict__ w, float eps, const float* __restrict__ cs,
+                                                                int rot_dims, const int32_t* __restrict__ pos,
+                                                                const int32_t* __restrict__ slot,
+                                                                const int32_t* __restrict__ block_table, int max_pages, int page_size,
+                                                                T* __restrict__ pool, const T* __restrict__ q, long long ldq, int H, int dn,
+                                                                T* __restrict__ qcat) {
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const float* row = dkv + (long long)t * ld;
+  const int p = pos[t];
+  const int page = block_table[(long long)slot[t] * max_pages + p / page_size];
+  T* dst = pool + ((long long)page * page_size + p % page_size) * (r + dr);
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < r; c += blockDim.x) ss = fmaf(row[c], row[c], ss);
+  ss = block_sum(ss, red);
+  const float rstd = 1.f / sqrtf(ss / (float)r + eps);
+  for (int c = threadIdx.x; c < r; c += blockDim.x) stf(dst + c, row[c] * rstd * ldf(w + c));
+  const int half = rot_dims >> 1;
+  const float* csr = cs + (long long)p * rot_dims;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float u = row[r + 2 * i], v = row[r + 2 * i + 1], co = csr[2 * i], si = csr[2 * i + 1];
+    stf(dst + r + 2 * i, u * co - v * si);
+    stf(dst + r + 2 * i + 1, v * co + u * si);
+  }
+  for (int c = rot_dims + threadIdx.x; c < dr; c += blockDim.x) stf(dst + r + c, row[r + c]);
+  // queries: every (head, pair) is one unit of work
+  for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
+    const int h = i / half, j = i - h * half;
+    const T* src = q + (long long)t * ldq + (long long)h * (dn + dr) + dn;
+    T* qd = qcat + ((long long)t * H + h) * (r + dr) + r;
+    const float u = ldf(src + 2 * j), v = ldf(src + 2 * j + 1), co = csr[2 * j], si = csr[2 * j + 1];
+    stf(qd + 2 * j, u * co - v * si);
+    stf(qd + 2 * j + 1, v * co + u * si);
+  }
+  const int rest = dr - rot_dims;
+  for (int i = threadIdx.x; i < H * rest; i += blockDim.x) {
+    const int h = i / rest, c = rot_dims + (i - h * rest);
+    stf(qcat + ((long long)t * H + h) * (r + dr) + r + c, ldf(q + (long long)t * ldq + (long long)h * (dn + dr) + dn + c));
+  }
+}
+
 constexpr int kLatWarps = 4;
 constexpr int kLatMaxPerLane = 32;  // r <= 1024
 
@@ -157,6 +202,24 @@ extern "C" int omc_latent_kv_store(const float* dkv, long long ld, int T, int r,
                                                       block_table, max_pages, page_size, static_cast<TC*>(pool));
   }))
   return check_launch("omc_latent_kv_store");
+}
+
+extern "C" int omc_latent_rope_store(const float* dkv, long long ld, int T, int r, int dr, const void* w, float eps, const float* cs,
+                                     int rot_dims, const int32_t* pos, const int32_t* slot, const int32_t* block_table, int max_pages,
+                                     int page_size, void* pool, const void* q, long long ldq, int H, int dn, void* qcat, int dt,
+                                     void* stream) {
+  if (dkv == nullptr || w == nullptr || cs == nullptr || pos == nullptr || slot == nullptr || block_table == nullptr || pool == nullptr ||
+      q == nullptr || qcat == nullptr || T < 0 || r <= 0 || dr < 0 || rot_dims < 0 || rot_dims > dr || (rot_dims & 1) || page_size <= 0 ||
+      max_pages <= 0 || H <= 0 || dn < 0)
+    return set_error(OMC_ERR_ARG, "omc_latent_rope_store: bad argument");
+  if (T == 0) return OMC_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  OMC_DT_SWITCH(dt, TT, {
+    latent_rope_store_kernel<TT><<<T, 128, 0, st>>>(dkv, ld, r, dr, static_cast<const TT*>(w), eps, cs, rot_dims, pos, slot, block_table,
+                                                    max_pages, page_size, static_cast<TT*>(pool), static_cast<const TT*>(q), ldq, H, dn,
+                                                    static_cast<TT*>(qcat));
+  })
+  return check_launch("omc_latent_rope_store");
 }
 
 extern "C" int omc_rotary_q(const void* q32, int in_dt, long long ldq, int T, int H, int dn, int dr, const float* cs, int rot_dims,

@@ -120,6 +120,50 @@ __global__ void __launch_bounds__(128) moe_scatter_rows_kernel(const TT* __restr
   }
 }
 
+// plan + scatter of a small step (decode rows) in ONE single-CTA launch: segment starts and the tile table as in the plan kernel,
+// then row after row is copied to its places (the cursors live in shared memory).
+template <typename TT>
+__global__ void __launch_bounds__(256) moe_plan_scatter_small_kernel(int32_t* __restrict__ counts, int experts, int tile, int max_tiles,
+                                                                     int32_t* __restrict__ seg_start, int32_t* __restrict__ tile_group,
+                                                                     const TT* __restrict__ x, long long ldx, int T, int C,
+                                                                     const int32_t* __restrict__ ids, int top,
+                                                                     int32_t* __restrict__ slot_of, TT* __restrict__ xs, long long ldxs) {
+  extern __shared__ int32_t s_seg[];  // [experts]: next free row of every expert's segment
+  __shared__ int s_slot[32];
+  for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) tile_group[i] = -1;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tiles = 0;
+    for (int e = 0; e < experts; ++e) {
+      const int n = (counts[e] + tile - 1) / tile;
+      seg_start[e] = tiles * tile;
+      s_seg[e] = tiles * tile;
+      for (int i = 0; i < n && tiles + i < max_tiles; ++i) tile_group[tiles + i] = e;
+      tiles += n;
+      counts[e] = 0;
+    }
+    seg_start[experts] = tiles * tile;
+  }
+  __syncthreads();
+  for (int t = 0; t < T; ++t) {
+    if (threadIdx.x == 0) {
+      for (int k = 0; k < top; ++k) {
+        const int e = ids[(long long)t * top + k];
+        const int sl = e < experts ? s_seg[e]++ : -1;
+        s_slot[k] = sl;
+        slot_of[(long long)t * top + k] = sl;
+      }
+    }
+    __syncthreads();
+    for (int k = 0; k < top; ++k) {
+      const int sl = s_slot[k];
+      if (sl < 0) continue;
+      for (int c = threadIdx.x; c < C; c += blockDim.x) xs[(long long)sl * ldxs + c] = x[(long long)t * ldx + c];
+    }
+    __syncthreads();
+  }
+}
+
 template <typename TW, typename TB>
 __global__ void __launch_bounds__(256) moe_combine_norm_kernel(const float* __restrict__ ys, long long ldys,
                                                                const int32_t* __restrict__ slot_of, const float* __restrict__ w, int top,
@@ -200,6 +244,21 @@ extern "C" int omc_moe_scatter_rows(const void* x, int dt, long long ldx, int T,
                                                    static_cast<TT*>(xs), ldxs);
   })
   return check_launch("omc_moe_scatter_rows");
+}
+
+extern "C" int omc_moe_plan_scatter_small(int32_t* counts, int experts, int tile, int max_tiles, int32_t* seg_start, int32_t* tile_group,
+                                          const void* x, int dt, long long ldx, int T, int C, const int32_t* ids, int top, int32_t* slot_of,
+                                          void* xs, long long ldxs, void* stream) {
+  if (counts == nullptr || seg_start == nullptr || tile_group == nullptr || x == nullptr || ids == nullptr || slot_of == nullptr ||
+      xs == nullptr || experts <= 0 || experts > 8192 || tile <= 0 || max_tiles <= 0 || T < 0 || C <= 0 || top <= 0 || top > 32)
+    return set_error(OMC_ERR_ARG, "omc_moe_plan_scatter_small: bad argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  OMC_DT_SWITCH(dt, TT, {
+    moe_plan_scatter_small_kernel<TT><<<1, 256, experts * sizeof(int32_t), st>>>(counts, experts, tile, max_tiles, seg_start, tile_group,
+                                                                                static_cast<const TT*>(x), ldx, T, C, ids, top, slot_of,
+                                                                                static_cast<TT*>(xs), ldxs);
+  })
+  return check_launch("omc_moe_plan_scatter_small");
 }
 
 extern "C" int omc_moe_combine_norm(const float* ys, long long ldys, const int32_t* slot_of, const float* w, int top, const float* gate,

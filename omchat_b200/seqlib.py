@@ -27,6 +27,8 @@ SIGNATURES = {
     "omc_rms_rows": (_I, [_P, _L, _P, _I, _I, _F, _P, _I, _L, _I, _I, _P]),
     "omc_norm_residual": (_I, [_P, _L, _P, _I, _F, _P, _L, _P, _I, _L, _I, _I, _P]),
     "omc_latent_kv_store": (_I, [_P, _L, _I, _I, _I, _P, _I, _F, _P, _I, _P, _P, _P, _I, _I, _P, _I, _P]),
+    "omc_latent_rope_store": (_I, [_P, _L, _I, _I, _I, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P, _P, _L, _I, _I, _P, _I, _P]),
+    "omc_moe_plan_scatter_small": (_I, [_P, _I, _I, _I, _P, _P, _P, _I, _L, _I, _I, _P, _I, _P, _P, _L, _P]),
     "omc_rotary_q": (_I, [_P, _I, _L, _I, _I, _I, _I, _P, _I, _P, _P, _I, _I, _P]),
     "omc_latent_attn": (_I, [_P, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P, _P, _P, _F, _P, _P]),
     "omc_latent_attn_mma": (_I, [_P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _P, _I, _P, _F, _P, _I, _P, _P, _P]),
@@ -134,6 +136,28 @@ def latent_kv_store(dkv: torch.Tensor, r: int, dr: int, w: torch.Tensor, eps: fl
                                     _ptr(pos), _ptr(slot), _ptr(block_table), block_table.shape[1], page_size, _ptr(pool),
                                     _dt(pool), _stream())
     _check(rc, "omc_latent_kv_store")
+
+
+def latent_rope_store(dkv, r: int, dr: int, w, eps: float, cs, rot_dims: int, pos, slot, block_table, page_size: int, pool, q, H: int,
+                      dn: int, qcat):
+    """latent_kv_store + rotary_q in one launch (w, pool, q, qcat of one dtype)."""
+    _need_cuda(dkv, w, cs, pos, slot, block_table, pool, q, qcat)
+    assert dkv.dtype == torch.float32 and w.dtype == pool.dtype == q.dtype == qcat.dtype and q.stride(1) == 1
+    assert block_table.is_contiguous() and pool.is_contiguous() and qcat.is_contiguous() and pool.shape[-1] == r + dr
+    rc = load().omc_latent_rope_store(_ptr(dkv), dkv.stride(0), dkv.shape[0], r, dr, _ptr(w), eps, _ptr(cs), rot_dims, _ptr(pos), _ptr(slot),
+                                      _ptr(block_table), block_table.shape[1], page_size, _ptr(pool), _ptr(q), q.stride(0), H, dn,
+                                      _ptr(qcat), _dt(pool), _stream())
+    _check(rc, "omc_latent_rope_store")
+
+
+def moe_plan_scatter_small(counts, experts: int, tile: int, max_tiles: int, seg_start, tile_group, x, ids, top: int, slot_of, xs):
+    """moe_plan_tiles + moe_scatter_rows as one single-CTA launch (steps of a few rows)."""
+    _need_cuda(counts, seg_start, tile_group, x, ids, slot_of, xs)
+    assert x.dtype == xs.dtype
+    rc = load().omc_moe_plan_scatter_small(_ptr(counts), experts, tile, max_tiles, _ptr(seg_start), _ptr(tile_group), _ptr(x), _dt(x),
+                                           x.stride(0), x.shape[0], x.shape[1], _ptr(ids), top, _ptr(slot_of), _ptr(xs), xs.stride(0),
+                                           _stream())
+    _check(rc, "omc_moe_plan_scatter_small")
 
 
 def rotary_q(q32: torch.Tensor, H: int, dn: int, dr: int, cs: torch.Tensor, rot_dims: int, pos: torch.Tensor, qcat: torch.Tensor,

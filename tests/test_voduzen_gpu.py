@@ -189,6 +189,64 @@ def test_norm_kernels(dt):
     assert rel_err(xb, want) < (1e-5 if dt == torch.float32 else 1e-2)
 
 
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_fused_rope_store_equals_the_two_kernels_and_the_plain_formulas(dt):
+    g = torch.Generator().manual_seed(17)
+    T, H, dn, dr, r, dims, page = 23, 3, 10, 12, 20, 8, 8
+    dkv = torch.randn(T, r + dr, generator=g).to(DEV)
+    q = torch.randn(T, H * (dn + dr), generator=g).to(dt).to(DEV)
+    w = (1 + 0.1 * torch.randn(r, generator=g)).to(dt).to(DEV)
+    rot = {"dims": dims, "base": 100.0}
+    cos, sin = O.rotary_angles(rot, 64)
+    cs = torch.stack([cos, sin], dim=-1).float().contiguous().to(DEV)
+    pos = torch.arange(5, 5 + T, dtype=torch.int32, device=DEV)
+    slot = torch.zeros(T, dtype=torch.int32, device=DEV)
+    table = torch.tensor([[3, 1, 4, 2, 0]], dtype=torch.int32, device=DEV)
+    pools = [torch.zeros(5, page, r + dr, device=DEV, dtype=dt) for _ in range(2)]
+    qcats = [torch.zeros(T, H, r + dr, device=DEV, dtype=dt) for _ in range(2)]
+    seqlib.latent_kv_store(dkv, r, dr, w, 1e-5, cs, dims, pos, slot, table, page, pools[0])
+    seqlib.rotary_q(q, H, dn, dr, cs, dims, pos, qcats[0], r)
+    seqlib.latent_rope_store(dkv, r, dr, w, 1e-5, cs, dims, pos, slot, table, page, pools[1], q, H, dn, qcats[1])
+    assert torch.equal(pools[0], pools[1]) and torch.equal(qcats[0], qcats[1])
+    tol = 1e-5 if dt == torch.float32 else 1e-2
+    p = pos.cpu().long()
+    want_c = O.norm_plain(dkv[:, :r].double().cpu(), w.double().cpu(), 1e-5)
+    want_k = O.rotate_interleaved(dkv[:, r:].double().cpu().contiguous(), cos[p], sin[p])
+    rows = pools[1][table[0].long()].reshape(-1, r + dr)[5:5 + T]
+    assert rel_err(rows[:, :r], want_c) < tol and rel_err(rows[:, r:], want_k) < tol
+    want_q = O.rotate_interleaved(q.double().cpu().view(T, H, dn + dr)[..., dn:].contiguous(), cos[p], sin[p])
+    assert rel_err(qcats[1][..., r:], want_q) < tol and float(qcats[1][..., :r].abs().max()) == 0.0
+
+
+def test_small_step_row_sort_equals_plan_and_scatter():
+    g = torch.Generator().manual_seed(19)
+    T, C, E, top, tile = 9, 24, 5, 3, 64
+    x = torch.randn(T, C, generator=g).to(DEV)
+    ids = torch.stack([torch.randperm(E + 2, generator=g)[:top] for _ in range(T)]).to(torch.int32).to(DEV)   # ids >= E: identity
+    counts = torch.tensor([int((ids == e).sum()) for e in range(E)], dtype=torch.int32, device=DEV)
+    mt = seqlib.moe_max_tiles(T, top, E, tile)
+    outs = []
+    for fused in (False, True):
+        cnt, cur = counts.clone(), torch.zeros(E, dtype=torch.int32, device=DEV)
+        seg, grp = torch.zeros(E + 1, dtype=torch.int32, device=DEV), torch.zeros(mt, dtype=torch.int32, device=DEV)
+        slot_of, xs = torch.zeros(T, top, dtype=torch.int32, device=DEV), torch.zeros(mt * tile, C, device=DEV)
+        if fused:
+            seqlib.moe_plan_scatter_small(cnt, E, tile, mt, seg, grp, x, ids, top, slot_of, xs)
+        else:
+            seqlib.moe_plan_tiles(cnt, E, tile, mt, seg, cur, grp)
+            seqlib.moe_scatter_rows(x, ids, top, E, seg, cur, slot_of, xs)
+        assert int(cnt.abs().sum()) == 0                                  # counters are left zeroed for the next call
+        outs.append((seg.cpu(), grp.cpu()))
+        for t in range(T):                                                 # every copy sits in its expert's segment and holds the row
+            for k in range(top):
+                e, sl = int(ids[t, k]), int(slot_of[t, k])
+                if e >= E:
+                    assert sl == -1
+                else:
+                    assert int(seg[e]) <= sl < int(seg[e]) + int(counts[e]) and torch.equal(xs[sl], x[t]) and int(grp[sl // tile]) == e
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
 def test_router_matches_plain_choice_and_counts():
     g = torch.Generator().manual_seed(11)
     T, E, I, top = 50, 6, 3, 4
