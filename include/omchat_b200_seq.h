@@ -125,6 +125,68 @@ int omc_moe_combine_norm(const float* ys, long long ldys, const int32_t* slot_of
                          const float* ysh, long long ldysh, const void* nw, int nw_dt, float eps, float* h32, long long ldh,
                          void* xb, int xb_dt, long long ldxb, int T, int C, void* stream);
 
+/* omc_linear with a bias row: Y = act(alpha * X W^T + bias). bias [N] has the weights' dtype; batch item b reads bias + b * sbias.
+ * NULL bias: omc_linear. Not with a tile table. */
+int omc_linear_bias(const void* X, int x_dt, long long ldx, long long sx, const void* W, int w_dt, long long ldw, long long sw,
+                    void* Y, int y_dt, long long ldy, long long sy, int M, int N, int K, int batch, float alpha, int act,
+                    const int32_t* tile_group, long long group_stride, const void* bias, long long sbias, void* stream);
+
+/* Sublayer output -> residual stream -> next sublayer's input in one pass over the row:
+ *   y = y1, or with y2 != NULL the mean of two branches, each normed with a plain weight first:
+ *       y = (y1 / rms(y1) * wa + y2 / rms(y2) * wb) / 2
+ *   h32 += mult * y / rms(y) * (1 + w_post)
+ *   xb = h32 / rms(h32) * (1 + w_next); w_next NULL: xb = round(h32); xb NULL: skipped.
+ * rms(z) = sqrt(mean(z^2) + eps). y1 / y2 fp32; all weights of w_dt. */
+int omc_post_norm_residual(const float* y1, long long ld1, const void* wa, const float* y2, long long ld2, const void* wb,
+                           const void* w_post, int w_dt, float eps, float mult, float* h32, long long ldh, const void* w_next,
+                           void* xb, int xb_dt, long long ldxb, int rows, int C, void* stream);
+
+/* y[t, c] = act(z[t, c]) * z[t, n + c] for c < n: the two halves of a stacked gate | up projection. z fp32. */
+int omc_glu_mul(const float* z, long long ldz, int rows, int n, int act, void* y, int y_dt, long long ldy, void* stream);
+
+/* Causal convolution over time per channel, then silu, then optional unit vectors. Row t is position pos[t] of the request in
+ * state slot slot[t]; rows of one request are consecutive and ascending. w [ch, taps] of w_dt: the last tap multiplies the row
+ * itself, tap j the input taps - 1 - j positions back - an earlier row of the step, else state[slot][position % (taps - 1)][ch]
+ * (fp32 ring of the last taps - 1 inputs, updated by this call), else zero before position 0. Of the outputs the first
+ * unit_channels are divided, in groups of unit_group, by sqrt(sum of squares + unit_eps); the first scaled_channels of those are
+ * then multiplied by unit_mult. x / y fp32 (y may not alias x). */
+int omc_causal_conv_silu(const float* x, long long ldx, int T, int ch, const void* w, int w_dt, int taps, const int32_t* pos,
+                         const int32_t* slot, float* state, float* y, long long ldy, int unit_channels, int unit_group,
+                         float unit_eps, int scaled_channels, float unit_mult, void* stream);
+
+/* Linear-state recurrence per head with an fp32 state S [dim, vdim] in state[slot][head]:
+ *   S <- diag(g_t) S;  u_t = beta_t (v_t - S^T k_t) (beta != NULL) or v_t;  S <- S + k_t u_t^T;  o_t = S^T q_t.
+ * decay_mode 0: g = decay_const[head]; 1: g = exp(-exp(A_log[head]) softplus(a[t, head] + dt_bias[head])); 2: one decay per key
+ * channel, a [T, H * dim], dt_bias [H * dim]. beta raw [T, H], squashed by a sigmoid here. silu_in: q, k, v pass silu first.
+ * q / k [T, G * dim] (head h reads group h / (H / G)), v [T, H * vdim], out fp32 [T, H * vdim]. Portion i is rows
+ * row_begin[i] .. row_begin[i + 1] - 1 (device int32 [portions + 1]), all of slot[row_begin[i]]; a portion whose first row has
+ * position 0 starts from S = 0. Tokens are processed one after the other in every case. dim <= 256. */
+int omc_linear_state_scan(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv, int silu_in,
+                          int decay_mode, const float* decay_const, const float* a, long long lda, const float* A_log,
+                          const float* dt_bias, const float* beta, long long ldb, float* state, float* out, long long ldo,
+                          const int32_t* row_begin, int portions, const int32_t* pos, const int32_t* slot, int H, int G, int dim,
+                          int vdim, void* stream);
+
+/* y[t, g * n + c] = x[t, g * n + c] / sqrt(mean_c(x[t, g * n + :]^2) + eps) * w[c] * act(gate[t, g * n + c]) for g < groups.
+ * gate fp32 or NULL; gate_act 0: as is, 1: silu, 2: sigmoid. w [n] of w_dt, y of y_dt. */
+int omc_gated_rms_rows(const float* x, long long ldx, int rows, int groups, int n, const void* w, int w_dt, float eps,
+                       const float* gate, long long ldg, int gate_act, void* y, int y_dt, long long ldy, void* stream);
+
+/* Rows of a step for windowed attention: q_out[t] = q[t, :nq] / rms * wq (plain weight, over all query columns at once); the
+ * cache row of (slot[t], pos[t]) <- [k[t, :nk] / rms * wk | v[t, :nv]]. Pool [pages][page_size][nk + nv] and q_out of dtype dt. */
+int omc_qk_norm_kv_store(const float* q, long long ldq, int nq, const void* wq, const float* k, long long ldk, int nk, const void* wk,
+                         int w_dt, const float* v, long long ldv, int nv, float eps, int T, const int32_t* pos, const int32_t* slot,
+                         const int32_t* block_table, int max_pages, int page_size, void* pool, void* q_out, long long ldqo, int dt,
+                         void* stream);
+
+/* Sliding-window attention over such a pool: row t (position p of its slot) sees the keys j with 0 <= p - j < window.
+ * score = (q_h . k_j) * scale; softcap > 0: score = softcap * tanh(score / softcap); dist_bias != NULL (fp32 [window, H]):
+ * score += dist_bias[p - j][h]; softmax; out[t, h * dv + :] = sum_j p_j v_j. Query head h reads key/value head h / (H / G).
+ * q [T, >= H * d] and pool of dtype dt, out of out_dt. dv <= 256. */
+int omc_window_attn(const void* q, long long ldq, int T, int H, int G, int d, int dv, const void* pool, int dt,
+                    const int32_t* block_table, int max_pages, int page_size, const int32_t* pos, const int32_t* slot, int window,
+                    float scale, float softcap, const float* dist_bias, void* out, int out_dt, long long ldo, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -3,8 +3,9 @@
 Separate libraries, so that a process compiles only what its model needs:
   core  omchat_b200/_lib/libomchat_b200.so      tcgen05 GEMMs, flash attention, the persistent decode kernel, the vision tower's
                                                 row kernels, preprocessing (include/omchat_b200.h)
-  seq   omchat_b200/_lib/libomchat_b200_seq.so  sequence-step kernels: latent attention over a paged cache, fp32 residual row
-                                                kernels, the score-corrected router, the any-shape linear layer
+  seq   omchat_b200/_lib/libomchat_b200_seq.so  sequence-step kernels: latent and windowed attention over a paged cache, fp32
+                                                residual row kernels, the score-corrected router, the any-shape linear layer,
+                                                short convolutions and linear-state recurrences over state slots
                                                 (include/omchat_b200_seq.h); built with IEEE division / square root / exp
   dense omchat_b200/_lib/libomchat_b200_dense.so  the GEMM / row-kernel / sampling subset of core, for a process that has no core
                                                 library (lib.load_dense() prefers a built core library, which has the same symbols)
@@ -27,7 +28,7 @@ LIBDIR = PKG / "_lib"
 LIB = LIBDIR / "libomchat_b200.so"
 SEQ_LIB = LIBDIR / "libomchat_b200_seq.so"
 SOURCES = ["capi.cu", "gemm_sm100.cu", "gemm_skinny.cu", "gemm_stream.cu", "gemv.cu", "rowops.cu", "attention.cu", "attention_sm100.cu", "decode_mega.cu", "preprocess.cu", "model_capi.cu", "moe.cu"]
-SEQ_SOURCES = ["capi.cu", "linear_any.cu", "rownorm32.cu", "latent_attention.cu", "router_moe.cu"]
+SEQ_SOURCES = ["capi.cu", "linear_any.cu", "rownorm32.cu", "latent_attention.cu", "router_moe.cu", "state_mixers.cu", "window_attention.cu"]
 DENSE_LIB = LIBDIR / "libomchat_b200_dense.so"
 DENSE_SOURCES = ["capi.cu", "gemm_sm100.cu", "gemm_skinny.cu", "rowops.cu", "moe.cu"]  # a subset of SOURCES that links on its own
 BASE_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]

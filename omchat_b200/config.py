@@ -277,3 +277,148 @@ class VoduzenConfig:
                 "embedding": {"scale": self.embedding_scale}, "logit_scale": self.logit_scale, "norm": {"eps": self.norm_eps},
                 "layers": out_layers, "kv_page_size": self.kv_page_size, "eos_token_id": self.eos_token_id,
                 "pad_token_id": self.pad_token_id}
+
+
+# --------------------------------------------------------------------------------------------------------------------- Tifisun
+@dataclass
+class DeltaRuleSpec:
+    """Gated delta rule: a [dim, vdim] fp32 state per head, decayed, corrected towards the new value along the key, read by the
+    query. kv_heads query / key heads serve heads value heads. conv: taps of the causal per-channel convolution in front of
+    q, k, v. channel_decay: one decay per key channel (projected through `decay_rank` columns) instead of one per head;
+    gate_rank: the output gate is projected through that many columns and squashed by a sigmoid (None: one projection, silu)."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+    channel_decay: bool = False
+    decay_rank: Optional[int] = None
+    gate_rank: Optional[int] = None
+
+
+@dataclass
+class WindowAttentionSpec:
+    """Softmax attention over a sliding window of `window` keys (the row's own included), grouped heads, no rotation. Queries and
+    keys are RMS-normed over their whole projection; scores are scaled, soft-capped (softcap * tanh(s / softcap); 0 = off) and
+    get a learned bias by distance: `bias_rows` table rows, the first half one per distance, the rest logarithmic up to bias_max."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    window: int
+    softcap: float = 0.0
+    bias_max: float = 0.0
+
+    @staticmethod
+    def bucket(n: int, rows: int, far: float) -> int:
+        import math
+        half = rows // 2
+        if n < half:
+            return n
+        return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+
+
+@dataclass
+class DecayAttentionSpec:
+    """Linear attention with one constant decay per head: S <- decay_h S + k v^T, o = S^T q, silu on q, k, v."""
+    heads: int
+    dim: int
+    vdim: int
+    decay: List[float] = field(default_factory=list)
+
+
+@dataclass
+class ParallelMixerSpec:
+    left: WindowAttentionSpec
+    right: DecayAttentionSpec
+
+
+@dataclass
+class DenseMlpSpec:
+    """act(W_gate x + b) * (W_up x + b) -> W_down + b, act = tanh-form gelu."""
+    ff: int
+
+
+@dataclass
+class TifisunLayerSpec:
+    type: str                      # 'delta' | 'channel_delta' | 'parallel'
+    mixer: object                  # DeltaRuleSpec | ParallelMixerSpec
+    mlp: Optional[DenseMlpSpec]
+    weights_of: Optional[int] = None   # the layer whose tensors this one uses (its cache and state are its own)
+
+
+
+@dataclass
+class TifisunConfig:
+    model_type: str = "tifisun"
+    vocab_size: int = 0
+    hidden_size: int = 0
+    embedding_scale: float = 1.0
+    residual_mult: float = 1.0
+    norm_eps: float = 1e-6
+    layers: List[TifisunLayerSpec] = field(default_factory=list)
+    kv_page_size: int = 64       # engine knob: tokens per cache page
+    eos_token_id: int = -1
+    pad_token_id: int = 0
+
+    MIXERS = ("delta", "channel_delta", "parallel")
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "TifisunConfig":
+        layers = []
+        for i, ld in enumerate(d["layers"]):
+            typ, m = ld["type"], ld["mixer"]
+            if typ not in cls.MIXERS:
+                raise ValueError(f"layer {i}: unknown mixer type {typ!r}")
+            if typ == "parallel":
+                l, r = m["left"], m["right"]
+                left = WindowAttentionSpec(heads=int(l["heads"]), kv_heads=int(l.get("kv_heads", l["heads"])), dim=int(l["dim"]),
+                                           vdim=int(l["vdim"]), scale=float(l["scale"]), window=int(l["mask"]["size"]),
+                                           softcap=float(l.get("softcap") or 0.0), bias_max=float(l.get("bias_max") or 0.0))
+                right = DecayAttentionSpec(heads=int(r["heads"]), dim=int(r["dim"]), vdim=int(r["vdim"]),
+                                           decay=[float(x) for x in r["decay"]])
+                if left.heads % left.kv_heads or len(right.decay) != right.heads or left.window < 1:
+                    raise ValueError(f"layer {i}: inconsistent mixer sizes")
+                mix = ParallelMixerSpec(left, right)
+            else:
+                mix = DeltaRuleSpec(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]),
+                                    vdim=int(m["vdim"]), conv=int(m["conv"]), channel_decay=typ == "channel_delta",
+                                    decay_rank=int(m["decay_rank"]) if m.get("decay_rank") else None,
+                                    gate_rank=int(m["gate_rank"]) if m.get("gate_rank") else None)
+                if mix.heads % mix.kv_heads or mix.conv < 1:
+                    raise ValueError(f"layer {i}: inconsistent mixer sizes")
+            md = ld.get("mlp")
+            if md and md.get("kind", "dense") != "dense":
+                raise ValueError(f"layer {i}: unknown feed-forward kind {md.get('kind')!r}")
+            wo = ld.get("weights_of")
+            if wo is not None and not (0 <= int(wo) < len(d["layers"]) and int(wo) != i and d["layers"][int(wo)]["type"] == typ):
+                raise ValueError(f"layer {i}: weights_of must name another layer of the same type")
+            layers.append(TifisunLayerSpec(type=typ, mixer=mix, mlp=DenseMlpSpec(ff=int(md["ff"])) if md else None,
+                                           weights_of=int(wo) if wo is not None else None))
+        return cls(vocab_size=int(d["vocab"]), hidden_size=int(d["width"]),
+                   embedding_scale=float((d.get("embedding") or {}).get("scale", 1.0)),
+                   residual_mult=float(d.get("residual_mult", 1.0)), norm_eps=float((d.get("norm") or {}).get("eps", 1e-6)),
+                   layers=layers, kv_page_size=int(d.get("kv_page_size", 64)), eos_token_id=int(d.get("eos_token_id", -1)),
+                   pad_token_id=int(d.get("pad_token_id", 0)))
+
+    def to_dict(self) -> dict:
+        """The config.json form (round-trips through from_dict)."""
+        out = []
+        for l in self.layers:
+            if l.type == "parallel":
+                a, b = l.mixer.left, l.mixer.right
+                md = {"left": {"bias_max": a.bias_max, "dim": a.dim, "heads": a.heads, "kv_heads": a.kv_heads,
+                               "mask": {"size": a.window}, "scale": a.scale, "softcap": a.softcap, "vdim": a.vdim},
+                      "right": {"decay": list(b.decay), "dim": b.dim, "heads": b.heads, "vdim": b.vdim}}
+            else:
+                m = l.mixer
+                md = {"conv": m.conv, "dim": m.dim, "heads": m.heads, "kv_heads": m.kv_heads, "vdim": m.vdim}
+            e = {"type": l.type, "mixer": md, "mlp": {"ff": l.mlp.ff, "kind": "dense"} if l.mlp else None}
+            if l.weights_of is not None:
+                e["weights_of"] = l.weights_of
+            out.append(e)
+        return {"architecture": "Tifisun", "vocab": self.vocab_size, "width": self.hidden_size,
+                "embedding": {"scale": self.embedding_scale}, "residual_mult": self.residual_mult, "norm": {"eps": self.norm_eps},
+                "layers": out, "kv_page_size": self.kv_page_size, "eos_token_id": self.eos_token_id,
+                "pad_token_id": self.pad_token_id}

@@ -21,6 +21,8 @@ struct LinearArgs {
   int M, N, K;
   float alpha;
   int act;
+  const void* bias;  // [N] of the weights' dtype, added before the activation (NULL: none); batch item b reads bias + b * sbias
+  long long sbias;
 };
 
 __device__ __forceinline__ float apply_act(float z, int act) {
@@ -77,7 +79,7 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(LinearArgs a) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
-      if (n < a.N) stf(Y + (long long)m * a.ldy + n, apply_act(acc[i][j] * a.alpha, a.act));
+      if (n < a.N) stf(Y + (long long)m * a.ldy + n, apply_act(acc[i][j] * a.alpha + (a.bias != nullptr ? ldf(static_cast<const TW*>(a.bias) + blockIdx.z * a.sbias + n) : 0.f), a.act));
     }
   }
 }
@@ -167,7 +169,9 @@ __global__ void __launch_bounds__(256) linear_mma_kernel(LinearArgs a) {
         const int m = m0 + wm * 64 + mm * 16 + g + 8 * hh;
         const int n = n0 + wn * 32 + nn * 8 + 2 * t4;
         if (m >= a.M || n >= a.N) continue;
-        const float v0 = apply_act(acc[mm][nn][2 * hh] * a.alpha, a.act), v1 = apply_act(acc[mm][nn][2 * hh + 1] * a.alpha, a.act);
+        const bf16_t* bias = a.bias != nullptr ? static_cast<const bf16_t*>(a.bias) + blockIdx.z * a.sbias : nullptr;
+        const float b0 = bias != nullptr ? ldf(bias + n) : 0.f, b1 = (bias != nullptr && n + 1 < a.N) ? ldf(bias + n + 1) : 0.f;
+        const float v0 = apply_act(acc[mm][nn][2 * hh] * a.alpha + b0, a.act), v1 = apply_act(acc[mm][nn][2 * hh + 1] * a.alpha + b1, a.act);
         TY* dst = Y + (long long)m * a.ldy + n;
         if (pair_ok && n + 1 < a.N) {
           store_pair(dst, v0, v1);
@@ -202,9 +206,10 @@ static int launch_linear(const LinearArgs& a, int y_dt, int batch, cudaStream_t 
 
 }  // namespace omc
 
-extern "C" int omc_linear(const void* X, int x_dt, long long ldx, long long sx, const void* W, int w_dt, long long ldw,
-                          long long sw, void* Y, int y_dt, long long ldy, long long sy, int M, int N, int K, int batch,
-                          float alpha, int act, const int32_t* tile_group, long long group_stride, void* stream) {
+extern "C" int omc_linear_bias(const void* X, int x_dt, long long ldx, long long sx, const void* W, int w_dt, long long ldw,
+                               long long sw, void* Y, int y_dt, long long ldy, long long sy, int M, int N, int K, int batch,
+                               float alpha, int act, const int32_t* tile_group, long long group_stride, const void* bias,
+                               long long sbias, void* stream) {
   using namespace omc;
   if (X == nullptr || W == nullptr || Y == nullptr || N <= 0 || K <= 0 || M < 0 || batch <= 0)
     return set_error(OMC_ERR_ARG, "omc_linear: bad argument");
@@ -212,7 +217,8 @@ extern "C" int omc_linear(const void* X, int x_dt, long long ldx, long long sx, 
   if (tile_group != nullptr && batch != 1) return set_error(OMC_ERR_ARG, "omc_linear: a tile table excludes a batch");
   if ((long long)((M + kLinBM - 1) / kLinBM) > 65535 || batch > 65535)
     return set_error(OMC_ERR_SHAPE, "omc_linear: more than 65535 row tiles or batch items");
-  LinearArgs a{X, W, Y, ldx, sx, ldw, sw, ldy, sy, group_stride, tile_group, M, N, K, alpha, act};
+  if (bias != nullptr && tile_group != nullptr) return set_error(OMC_ERR_ARG, "omc_linear: a bias excludes a tile table");
+  LinearArgs a{X, W, Y, ldx, sx, ldw, sw, ldy, sy, group_stride, tile_group, M, N, K, alpha, act, bias, sbias};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (x_dt == OMC_DT_F32 && w_dt == OMC_DT_F32) return launch_linear<float, float>(a, y_dt, batch, st);
   if (x_dt == OMC_DT_F32 && w_dt == OMC_DT_BF16) return launch_linear<float, bf16_t>(a, y_dt, batch, st);
@@ -222,4 +228,11 @@ extern "C" int omc_linear(const void* X, int x_dt, long long ldx, long long sx, 
     return launch_linear<bf16_t, bf16_t>(a, y_dt, batch, st);
   }
   return set_error(OMC_ERR_ARG, "omc_linear: operand dtypes must be (f32, f32), (f32, bf16) or (bf16, bf16)");
+}
+
+extern "C" int omc_linear(const void* X, int x_dt, long long ldx, long long sx, const void* W, int w_dt, long long ldw,
+                          long long sw, void* Y, int y_dt, long long ldy, long long sy, int M, int N, int K, int batch,
+                          float alpha, int act, const int32_t* tile_group, long long group_stride, void* stream) {
+  return omc_linear_bias(X, x_dt, ldx, sx, W, w_dt, ldw, sw, Y, y_dt, ldy, sy, M, N, K, batch, alpha, act, tile_group, group_stride,
+                         nullptr, 0, stream);
 }

@@ -58,6 +58,78 @@ __global__ void __launch_bounds__(256) norm_residual_kernel(const float* __restr
   }
 }
 
+
+// Sublayer output -> residual stream -> next sublayer's input, one CTA per row, the row staged in shared memory:
+//   y = y1                                               (y2 == NULL)
+//   y = (y1 / rms(y1) * wa + y2 / rms(y2) * wb) / 2      (two mixers side by side, each normed with a plain weight first)
+//   h32 += mult * y / rms(y) * (1 + w_post)
+//   xb = h32 / rms(h32) * (1 + w_next)   (w_next == NULL: xb = round(h32); xb == NULL: nothing)
+template <typename TW, typename TB>
+__global__ void __launch_bounds__(256) post_norm_residual_kernel(const float* __restrict__ y1, long long ld1, const TW* __restrict__ wa,
+                                                                 const float* __restrict__ y2, long long ld2, const TW* __restrict__ wb,
+                                                                 const TW* __restrict__ w_post, float eps, float mult,
+                                                                 float* __restrict__ h32, long long ldh, const TW* __restrict__ w_next,
+                                                                 TB* __restrict__ xb, long long ldxb, int C) {
+  extern __shared__ float row[];  // [C]
+  __shared__ float red[33];
+  const long long t = blockIdx.x;
+  float s1 = 0.f, s2 = 0.f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float a = y1[t * ld1 + c];
+    s1 = fmaf(a, a, s1);
+    if (y2 != nullptr) {
+      const float b = y2[t * ld2 + c];
+      s2 = fmaf(b, b, s2);
+    }
+  }
+  s1 = block_sum(s1, red);
+  float ss = 0.f;
+  if (y2 != nullptr) {
+    s2 = block_sum(s2, red);
+    const float r1 = 1.f / sqrtf(s1 / (float)C + eps), r2 = 1.f / sqrtf(s2 / (float)C + eps);
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+      const float v = 0.5f * (y1[t * ld1 + c] * r1 * ldf(wa + c) + y2[t * ld2 + c] * r2 * ldf(wb + c));
+      row[c] = v;
+      ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+  } else {
+    for (int c = threadIdx.x; c < C; c += blockDim.x) row[c] = y1[t * ld1 + c];
+    ss = s1;
+  }
+  const float rstd = 1.f / sqrtf(ss / (float)C + eps);
+  float sh = 0.f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {   // every thread rereads only what it wrote
+    const float v = h32[t * ldh + c] + mult * (row[c] * rstd * (1.f + ldf(w_post + c)));
+    h32[t * ldh + c] = v;
+    row[c] = v;
+    sh = fmaf(v, v, sh);
+  }
+  if (xb == nullptr) return;
+  if (w_next == nullptr) {
+    for (int c = threadIdx.x; c < C; c += blockDim.x) stf(xb + t * ldxb + c, row[c]);
+    return;
+  }
+  sh = block_sum(sh, red);
+  const float rn = 1.f / sqrtf(sh / (float)C + eps);
+  for (int c = threadIdx.x; c < C; c += blockDim.x) stf(xb + t * ldxb + c, row[c] * rn * (1.f + ldf(w_next + c)));
+}
+
+// out = act(gate) * up over the two halves of a stacked projection: z [rows, 2 * n] fp32 -> out [rows, n].
+template <typename TY>
+__global__ void __launch_bounds__(256) glu_mul_kernel(const float* __restrict__ z, long long ldz, int n, int act, TY* __restrict__ y,
+                                                      long long ldy, long long total) {
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= total) return;
+  const long long t = e / n;
+  const int c = (int)(e - t * n);
+  float g = z[t * ldz + c];
+  const float u = z[t * ldz + n + c];
+  if (act == OMC_ACT_GELU_TANH) g = 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  else if (act == OMC_ACT_RELU2) g = fmaxf(g, 0.f) * fmaxf(g, 0.f);
+  stf(y + t * ldy + c, g * u);
+}
+
 }  // namespace omc
 
 using namespace omc;
@@ -94,4 +166,33 @@ extern "C" int omc_norm_residual(const float* y, long long ldy, const void* w, i
     norm_residual_kernel<TW, TB><<<rows, 256, 0, st>>>(y, ldy, static_cast<const TW*>(w), eps, h32, ldh, static_cast<TB*>(xb), ldxb, C);
   }))
   return check_launch("omc_norm_residual");
+}
+
+extern "C" int omc_post_norm_residual(const float* y1, long long ld1, const void* wa, const float* y2, long long ld2, const void* wb,
+                                      const void* w_post, int w_dt, float eps, float mult, float* h32, long long ldh,
+                                      const void* w_next, void* xb, int xb_dt, long long ldxb, int rows, int C, void* stream) {
+  if (y1 == nullptr || w_post == nullptr || h32 == nullptr || rows < 0 || C <= 0 || (y2 != nullptr && (wa == nullptr || wb == nullptr)))
+    return set_error(OMC_ERR_ARG, "omc_post_norm_residual: bad argument");
+  if (rows == 0) return OMC_OK;
+  const size_t smem = (size_t)C * sizeof(float);
+  if (smem > 200 * 1024) return set_error(OMC_ERR_SHAPE, "omc_post_norm_residual: row too wide for shared memory");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  OMC_DT_SWITCH(w_dt, TW, OMC_DT_SWITCH(xb_dt, TB, {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(post_norm_residual_kernel<TW, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    post_norm_residual_kernel<TW, TB><<<rows, 256, smem, st>>>(y1, ld1, static_cast<const TW*>(wa), y2, ld2, static_cast<const TW*>(wb),
+                                                               static_cast<const TW*>(w_post), eps, mult, h32, ldh,
+                                                               static_cast<const TW*>(w_next), static_cast<TB*>(xb), ldxb, C);
+  }))
+  return check_launch("omc_post_norm_residual");
+}
+
+extern "C" int omc_glu_mul(const float* z, long long ldz, int rows, int n, int act, void* y, int y_dt, long long ldy, void* stream) {
+  if (z == nullptr || y == nullptr || rows < 0 || n <= 0) return set_error(OMC_ERR_ARG, "omc_glu_mul: bad argument");
+  if (rows == 0) return OMC_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long total = (long long)rows * n;
+  OMC_DT_SWITCH(y_dt, TY, {
+    glu_mul_kernel<TY><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(z, ldz, n, act, static_cast<TY*>(y), ldy, total);
+  })
+  return check_launch("omc_glu_mul");
 }

@@ -1,0 +1,303 @@
+// Mixers that carry a fixed-size state per sequence instead of a growing cache: a short causal convolution per channel whose
+// last inputs are state, and the family of linear-state recurrences
+//     S <- diag(g_t) S;   u_t = beta_t (v_t - S^T k_t)  (delta rule)  or  u_t = v_t  (plain outer-product sum);
+//     S <- S + k_t u_t^T;   o_t = S^T q_t
+// with the decay g_t constant per head, one per token and head, or one per token, head and key channel, and the gated RMS norm
+// that follows them. Rows of a step are addressed by (slot, position); the rows of one request are consecutive and ascending.
+// A portion that starts at position 0 starts from a zero state, so a slot needs no clearing when it is handed to a new request.
+// Everything here is fp32: state, decays and their logarithms, softplus / exponentials, step sizes, unit norms.
+//
+// The recurrence is evaluated token by token in every case - prompt portions and single decoded tokens run the same
+// instructions in the same order, which makes the result independent of how a prompt is cut. Its parallelism is over the
+// independent COLUMNS of S: column j of a head's state only ever meets v[:, j], so a CTA owns 32 columns of one head of one
+// portion, four lanes share a column (each holds dim / 4 state elements in registers) and finish the two dot products of a
+// token with two shuffles each. Tokens are staged 16 at a time in shared memory (decays, sigmoid and unit scaling applied on
+// the way in), so the sequential loop touches registers and shared memory only.
+#include "seq_common.cuh"
+
+namespace omc {
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+
+// ---- causal convolution + silu (+ unit vectors) ---------------------------------------------------------------------------
+// One CTA per row. Tap j of `taps` multiplies the input `taps - 1 - j` positions back: an earlier row of the same step when that
+// row belongs to the same request, else the state ring state[slot][position % (taps - 1)][channel], else (before position 0) zero.
+template <typename TW>
+__global__ void __launch_bounds__(256) causal_conv_silu_kernel(const float* __restrict__ x, long long ldx, int ch,
+                                                               const TW* __restrict__ w, int taps, const int32_t* __restrict__ pos,
+                                                               const int32_t* __restrict__ slot, const float* __restrict__ state,
+                                                               float* __restrict__ y, long long ldy, int unit_channels,
+                                                               int unit_group, float unit_eps, int scaled_channels, float unit_mult) {
+  extern __shared__ float row[];  // [ch]
+  const int t = blockIdx.x;
+  const int p = pos[t], s = slot[t], R = taps - 1;
+  for (int c = threadIdx.x; c < ch; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int back = R - j, sp = p - back;
+      if (sp < 0) continue;
+      float xv;
+      if (back == 0 || (t - back >= 0 && slot[t - back] == s)) xv = x[(long long)(t - back) * ldx + c];
+      else xv = state[((long long)s * R + sp % R) * ch + c];
+      acc = fmaf(ldf(w + (long long)c * taps + j), xv, acc);
+    }
+    row[c] = silu_f(acc);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int groups = unit_group > 0 ? unit_channels / unit_group : 0;
+  for (int g = warp; g < groups; g += nw) {
+    float ss = 0.f;
+    for (int c = lane; c < unit_group; c += 32) {
+      const float v = row[g * unit_group + c];
+      ss = fmaf(v, v, ss);
+    }
+    ss = seq_warp_sum(ss);
+    const float f = (1.f / sqrtf(ss + unit_eps)) * (g * unit_group < scaled_channels ? unit_mult : 1.f);
+    for (int c = lane; c < unit_group; c += 32) row[g * unit_group + c] *= f;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < ch; c += blockDim.x) y[(long long)t * ldy + c] = row[c];
+}
+
+// The last taps - 1 inputs of every request of the step go into its ring (rows that are followed by taps - 1 more rows of the
+// same request are not among them).
+__global__ void __launch_bounds__(256) conv_state_save_kernel(const float* __restrict__ x, long long ldx, int ch, int R, int T,
+                                                              const int32_t* __restrict__ pos, const int32_t* __restrict__ slot,
+                                                              float* __restrict__ state) {
+  const int t = blockIdx.x;
+  const int s = slot[t];
+  if (t + R < T && slot[t + R] == s) return;
+  float* dst = state + ((long long)s * R + pos[t] % R) * ch;
+  for (int c = threadIdx.x; c < ch; c += blockDim.x) dst[c] = x[(long long)t * ldx + c];
+}
+
+// ---- linear-state recurrence ----------------------------------------------------------------------------------------------
+constexpr int kScanCols = 32, kScanLanes = 4, kScanTok = 16;
+
+struct ScanArgs {
+  const float* q;      // [T, ldq]: head g of kv_heads at columns g * dim
+  const float* k;
+  const float* v;      // [T, ldv]: head h at columns h * vdim
+  long long ldq, ldk, ldv;
+  int silu_in;         // q, k, v pass silu on the way in
+  int decay_mode;      // 0: decay_const[h]; 1: a[t, h]; 2: a[t, h * dim + i]  (1, 2: g = exp(-exp(A_log[h]) softplus(a + dt_bias)))
+  const float* decay_const;
+  const float* a;
+  long long lda;
+  const float* A_log;    // fp32 [H]
+  const float* dt_bias;  // fp32 [H] (mode 1) or [H * dim] (mode 2)
+  const float* beta;     // raw [T, ldb]: beta = sigmoid; NULL: no delta correction (u = v)
+  long long ldb;
+  float* state;          // [slots][H][dim][vdim]
+  float* out;            // [T, ldo]
+  long long ldo;
+  const int32_t* row_begin;  // [P + 1] first row of every portion
+  const int32_t* pos;
+  const int32_t* slot;
+  int H, G, dim, vdim;
+};
+
+template <int DPT>
+__global__ void __launch_bounds__(kScanCols * kScanLanes) linear_state_scan_kernel(ScanArgs a) {
+  extern __shared__ float sm[];
+  const int dim = a.dim;
+  float* sk = sm;                          // [tok][dim]
+  float* sq = sk + kScanTok * dim;         // [tok][dim]
+  float* sg = sq + kScanTok * dim;         // [tok][dim] (mode 2) or [tok]
+  const int gw = a.decay_mode == 2 ? dim : 1;
+  float* sv = sg + kScanTok * gw;          // [tok][cols]
+  float* sb = sv + kScanTok * kScanCols;   // [tok]
+  const int h = blockIdx.y, kvh = h / (a.H / a.G);
+  const int col0 = blockIdx.x * kScanCols;
+  const int r0 = a.row_begin[blockIdx.z], r1 = a.row_begin[blockIdx.z + 1];
+  if (r1 <= r0) return;
+  const int tid = threadIdx.x, lane = tid & (kScanLanes - 1), col = col0 + (tid >> 2);
+  const bool col_ok = col < a.vdim;
+  float* S = a.state + (((long long)a.slot[r0] * a.H + h) * dim) * a.vdim;
+  float st[DPT];
+  const bool fresh = a.pos[r0] == 0;
+#pragma unroll
+  for (int r = 0; r < DPT; ++r) {
+    const int i = lane + kScanLanes * r;
+    st[r] = (!fresh && col_ok && i < dim) ? S[(long long)i * a.vdim + col] : 0.f;
+  }
+  const float A = a.decay_mode != 0 ? expf(a.A_log[h]) : 0.f;
+  const float gconst = a.decay_mode == 0 ? a.decay_const[h] : 1.f;
+  for (int c0 = r0; c0 < r1; c0 += kScanTok) {
+    const int n = min(kScanTok, r1 - c0);
+    __syncthreads();
+    for (int e = tid; e < n * dim; e += blockDim.x) {
+      const int tt = e / dim, i = e - tt * dim;
+      float kv = a.k[(long long)(c0 + tt) * a.ldk + kvh * dim + i], qv = a.q[(long long)(c0 + tt) * a.ldq + kvh * dim + i];
+      if (a.silu_in) {
+        kv = silu_f(kv);
+        qv = silu_f(qv);
+      }
+      sk[tt * dim + i] = kv;
+      sq[tt * dim + i] = qv;
+      if (a.decay_mode == 2)
+        sg[tt * dim + i] = expf(-A * softplus_f(a.a[(long long)(c0 + tt) * a.lda + h * dim + i] + a.dt_bias[h * dim + i]));
+    }
+    for (int e = tid; e < n * kScanCols; e += blockDim.x) {
+      const int tt = e / kScanCols, j = e - tt * kScanCols;
+      float vv = col0 + j < a.vdim ? a.v[(long long)(c0 + tt) * a.ldv + h * a.vdim + col0 + j] : 0.f;
+      if (a.silu_in) vv = silu_f(vv);
+      sv[e] = vv;
+    }
+    if (tid < n) {
+      sb[tid] = a.beta != nullptr ? sigmoid_f(a.beta[(long long)(c0 + tid) * a.ldb + h]) : 1.f;
+      if (a.decay_mode == 1) sg[tid] = expf(-A * softplus_f(a.a[(long long)(c0 + tid) * a.lda + h] + a.dt_bias[h]));
+      else if (a.decay_mode == 0) sg[tid] = gconst;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < n; ++tt) {
+      const float* kr = sk + tt * dim;
+      const float* qr = sq + tt * dim;
+      float dot = 0.f;
+      if (a.decay_mode == 2) {
+        const float* gr = sg + tt * dim;
+#pragma unroll
+        for (int r = 0; r < DPT; ++r) {
+          const int i = lane + kScanLanes * r;
+          if (i < dim) {
+            st[r] *= gr[i];
+            dot = fmaf(st[r], kr[i], dot);
+          }
+        }
+      } else {
+        const float g = sg[tt];
+#pragma unroll
+        for (int r = 0; r < DPT; ++r) {
+          const int i = lane + kScanLanes * r;
+          if (i < dim) {
+            st[r] *= g;
+            dot = fmaf(st[r], kr[i], dot);
+          }
+        }
+      }
+      float u = sv[tt * kScanCols + (tid >> 2)];
+      if (a.beta != nullptr) {
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        u = sb[tt] * (u - dot);
+      }
+      float o = 0.f;
+#pragma unroll
+      for (int r = 0; r < DPT; ++r) {
+        const int i = lane + kScanLanes * r;
+        if (i < dim) {
+          st[r] = fmaf(kr[i], u, st[r]);
+          o = fmaf(st[r], qr[i], o);
+        }
+      }
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (lane == 0 && col_ok) a.out[(long long)(c0 + tt) * a.ldo + h * a.vdim + col] = o;
+    }
+  }
+  if (col_ok) {
+#pragma unroll
+    for (int r = 0; r < DPT; ++r) {
+      const int i = lane + kScanLanes * r;
+      if (i < dim) S[(long long)i * a.vdim + col] = st[r];
+    }
+  }
+}
+
+// ---- gated RMS norm over groups of a row ----------------------------------------------------------------------------------
+// y[t, g * n + c] = x[t, g * n + c] / sqrt(mean_c x^2 + eps) * w[c] * act(gate[t, g * n + c]); a warp per group.
+template <typename TW, typename TY>
+__global__ void __launch_bounds__(256) gated_rms_kernel(const float* __restrict__ x, long long ldx, int groups, int n,
+                                                        const TW* __restrict__ w, float eps, const float* __restrict__ gate,
+                                                        long long ldg, int gate_act, TY* __restrict__ y, long long ldy) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const long long t = blockIdx.x;
+  for (int g = blockIdx.y * nw + warp; g < groups; g += nw * gridDim.y) {
+    const float* xr = x + t * ldx + (long long)g * n;
+    float ss = 0.f;
+    for (int c = lane; c < n; c += 32) ss = fmaf(xr[c], xr[c], ss);
+    ss = seq_warp_sum(ss);
+    const float rstd = 1.f / sqrtf(ss / (float)n + eps);
+    for (int c = lane; c < n; c += 32) {
+      float v = xr[c] * rstd * ldf(w + c);
+      if (gate != nullptr) {
+        const float z = gate[t * ldg + (long long)g * n + c];
+        v *= gate_act == 1 ? silu_f(z) : (gate_act == 2 ? sigmoid_f(z) : z);
+      }
+      stf(y + t * ldy + (long long)g * n + c, v);
+    }
+  }
+}
+
+}  // namespace omc
+
+using namespace omc;
+
+extern "C" int omc_causal_conv_silu(const float* x, long long ldx, int T, int ch, const void* w, int w_dt, int taps,
+                                    const int32_t* pos, const int32_t* slot, float* state, float* y, long long ldy,
+                                    int unit_channels, int unit_group, float unit_eps, int scaled_channels, float unit_mult,
+                                    void* stream) {
+  if (x == nullptr || w == nullptr || pos == nullptr || slot == nullptr || y == nullptr || T < 0 || ch <= 0 || taps < 1 ||
+      (taps > 1 && state == nullptr) || unit_channels < 0 || unit_channels > ch || (unit_channels > 0 && (unit_group <= 0 || unit_channels % unit_group)))
+    return set_error(OMC_ERR_ARG, "omc_causal_conv_silu: bad argument");
+  if (T == 0) return OMC_OK;
+  if ((size_t)ch * sizeof(float) > 200 * 1024) return set_error(OMC_ERR_SHAPE, "omc_causal_conv_silu: too many channels for one row in shared memory");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)ch * sizeof(float);
+  OMC_DT_SWITCH(w_dt, TW, {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(causal_conv_silu_kernel<TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    causal_conv_silu_kernel<TW><<<T, 256, smem, st>>>(x, ldx, ch, static_cast<const TW*>(w), taps, pos, slot, state, y, ldy,
+                                                      unit_channels, unit_group, unit_eps, scaled_channels, unit_mult);
+  })
+  if (taps > 1) conv_state_save_kernel<<<T, 256, 0, st>>>(x, ldx, ch, taps - 1, T, pos, slot, state);
+  return check_launch("omc_causal_conv_silu");
+}
+
+extern "C" int omc_linear_state_scan(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv,
+                                     int silu_in, int decay_mode, const float* decay_const, const float* a, long long lda,
+                                     const float* A_log, const float* dt_bias, const float* beta, long long ldb, float* state,
+                                     float* out, long long ldo, const int32_t* row_begin, int portions, const int32_t* pos,
+                                     const int32_t* slot, int H, int G, int dim, int vdim, void* stream) {
+  if (q == nullptr || k == nullptr || v == nullptr || state == nullptr || out == nullptr || row_begin == nullptr || pos == nullptr ||
+      slot == nullptr || portions < 0 || H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || decay_mode < 0 || decay_mode > 2 ||
+      (decay_mode == 0 && decay_const == nullptr) || (decay_mode != 0 && (a == nullptr || A_log == nullptr || dt_bias == nullptr)))
+    return set_error(OMC_ERR_ARG, "omc_linear_state_scan: bad argument");
+  if (portions == 0) return OMC_OK;
+  if (dim > 256) return set_error(OMC_ERR_SHAPE, "omc_linear_state_scan: key width above 256");
+  if (portions > 65535 || H > 65535) return set_error(OMC_ERR_SHAPE, "omc_linear_state_scan: more than 65535 portions or heads");
+  ScanArgs s{q, k, v, ldq, ldk, ldv, silu_in, decay_mode, decay_const, a, lda, A_log, dt_bias, beta, ldb, state, out, ldo,
+             row_begin, pos, slot, H, G, dim, vdim};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t smem = sizeof(float) * ((size_t)kScanTok * dim * 2 + (size_t)kScanTok * (decay_mode == 2 ? dim : 1) + kScanTok * kScanCols + kScanTok);
+  dim3 grid((vdim + kScanCols - 1) / kScanCols, H, portions);
+  const int threads = kScanCols * kScanLanes;
+  if (dim <= 32) linear_state_scan_kernel<8><<<grid, threads, smem, st>>>(s);
+  else if (dim <= 64) linear_state_scan_kernel<16><<<grid, threads, smem, st>>>(s);
+  else if (dim <= 128) linear_state_scan_kernel<32><<<grid, threads, smem, st>>>(s);
+  else {
+    static bool attr_done[kMaxDevices] = {};
+    if (smem > 48 * 1024 && !attr_done[cur_device()]) {
+      cudaFuncSetAttribute(linear_state_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+      attr_done[cur_device()] = true;
+    }
+    linear_state_scan_kernel<64><<<grid, threads, smem, st>>>(s);
+  }
+  return check_launch("omc_linear_state_scan");
+}
+
+extern "C" int omc_gated_rms_rows(const float* x, long long ldx, int rows, int groups, int n, const void* w, int w_dt, float eps,
+                                  const float* gate, long long ldg, int gate_act, void* y, int y_dt, long long ldy, void* stream) {
+  if (x == nullptr || w == nullptr || y == nullptr || rows < 0 || groups <= 0 || n <= 0 || gate_act < 0 || gate_act > 2)
+    return set_error(OMC_ERR_ARG, "omc_gated_rms_rows: bad argument");
+  if (rows == 0) return OMC_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int gy = groups > 8 ? (groups + 7) / 8 : 1;
+  OMC_DT_SWITCH(w_dt, TW, OMC_DT_SWITCH(y_dt, TY, {
+    gated_rms_kernel<TW, TY><<<dim3(rows, gy > 65535 ? 65535 : gy), 256, 0, st>>>(x, ldx, groups, n, static_cast<const TW*>(w), eps,
+                                                                                 gate, ldg, gate_act, static_cast<TY*>(y), ldy);
+  }))
+  return check_launch("omc_gated_rms_rows");
+}

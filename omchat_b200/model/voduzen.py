@@ -27,6 +27,7 @@ import torch
 from .. import lib, seqlib
 from ..config import LatentAttentionSpec, RouterMoeSpec, VoduzenConfig
 from .paged_cache import PagedLatentCache
+from .seq_linear import TENSOR_GEMM_MIN_WEIGHT, dense_linear
 
 
 # ------------------------------------------------------------------------------------------------------------------- weights
@@ -164,12 +165,6 @@ def random_state_dict(cfg: VoduzenConfig, seed: int = 0, std: float = 0.05) -> D
 
 
 # ------------------------------------------------------------------------------------------------------------------- decoder
-# Matrices with at least this many elements go through the tcgen05 GEMM of the core library when the operands are bf16 and the
-# dimensions are multiples of 8; below it a launch is latency-bound either way and the FMA kernel needs no second library.
-# Steps of up to 64 rows stream the weights through the skinny GEMM from a much smaller size on: the FMA kernel walks K with one
-# 64-row tile per CTA, which leaves a decode step waiting on a handful of CTAs.
-TENSOR_GEMM_MIN_WEIGHT = 1 << 20
-SKINNY_GEMM_MIN_WEIGHT = 1 << 17
 SMALL_STEP_ROWS = 4    # steps of up to this many rows sort their rows by expert in one single-CTA launch (32 rows: 0.07 ms per layer slower than the two kernels)
 
 
@@ -210,15 +205,7 @@ class VoduzenDecoder:
     # ---- linear layers
     def _linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, act: int = seqlib.ACT_NONE, alpha: float = 1.0):
         """act(alpha * x @ w^T) -> [rows, N] of out_dtype."""
-        M, K = x.shape
-        N = w.shape[0]
-        big = N * K >= (SKINNY_GEMM_MIN_WEIGHT if M <= lib.SKINNY_MAX_M else TENSOR_GEMM_MIN_WEIGHT)
-        if (self.tensor_gemm and x.dtype == torch.bfloat16 and big and N % 8 == 0 and K % 8 == 0
-                and x.stride(0) % 8 == 0 and (act == seqlib.ACT_NONE or (act == seqlib.ACT_RELU2 and out_dtype == torch.bfloat16))):
-            y = lib.gemm(x, w, out_f32=out_dtype == torch.float32, epi=lib.EPI_RELU2 if act == seqlib.ACT_RELU2 else lib.EPI_NONE)
-            return y if alpha == 1.0 else y.mul_(alpha)
-        out = torch.empty(M, N, device=x.device, dtype=out_dtype)
-        return seqlib.linear(x, w, out, alpha=alpha, act=act)
+        return dense_linear(x, w, out_dtype, tensor_gemm=self.tensor_gemm, act=act, alpha=alpha)
 
     # ---- sublayers
     def _mixer(self, li: int, xb: torch.Tensor, pos, slot, cache: PagedLatentCache, plans: Optional[dict] = None) -> torch.Tensor:

@@ -23,6 +23,14 @@ LINEAR_TILE = 64  # rows per tile of omc_linear's tile -> group table
 SIGNATURES = {
     "omc_last_error": (c_char_p, []),
     "omc_linear": (_I, [_P, _I, _L, _L, _P, _I, _L, _L, _P, _I, _L, _L, _I, _I, _I, _I, _F, _I, _P, _L, _P]),
+    "omc_linear_bias": (_I, [_P, _I, _L, _L, _P, _I, _L, _L, _P, _I, _L, _L, _I, _I, _I, _I, _F, _I, _P, _L, _P, _L, _P]),
+    "omc_post_norm_residual": (_I, [_P, _L, _P, _P, _L, _P, _P, _I, _F, _F, _P, _L, _P, _P, _I, _L, _I, _I, _P]),
+    "omc_glu_mul": (_I, [_P, _L, _I, _I, _I, _P, _I, _L, _P]),
+    "omc_causal_conv_silu": (_I, [_P, _L, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _F, _I, _F, _P]),
+    "omc_linear_state_scan": (_I, [_P, _L, _P, _L, _P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _L, _P, _P, _L, _P, _I, _P, _P, _I, _I, _I, _I, _P]),
+    "omc_gated_rms_rows": (_I, [_P, _L, _I, _I, _I, _P, _I, _F, _P, _L, _I, _P, _I, _L, _P]),
+    "omc_qk_norm_kv_store": (_I, [_P, _L, _I, _P, _P, _L, _I, _P, _I, _P, _L, _I, _F, _I, _P, _P, _P, _I, _I, _P, _P, _L, _I, _P]),
+    "omc_window_attn": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P, _P, _I, _F, _F, _P, _P, _I, _L, _P]),
     "omc_embed_scale": (_I, [_P, _I, _P, _I, _I, _I, _F, _P, _L, _P, _I, _L, _P]),
     "omc_rms_rows": (_I, [_P, _L, _P, _I, _I, _F, _P, _I, _L, _I, _I, _P]),
     "omc_norm_residual": (_I, [_P, _L, _P, _I, _F, _P, _L, _P, _I, _L, _I, _I, _P]),
@@ -82,8 +90,8 @@ def _dt(t: Optional[torch.Tensor]) -> int:
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, M: Optional[int] = None, N: Optional[int] = None,
            K: Optional[int] = None, ldx: Optional[int] = None, ldw: Optional[int] = None, ldy: Optional[int] = None,
            batch: int = 1, sx: int = 0, sw: int = 0, sy: int = 0, alpha: float = 1.0, act: int = ACT_NONE,
-           tile_group: Optional[torch.Tensor] = None, group_stride: int = 0) -> torch.Tensor:
-    """out = act(alpha * x @ w^T). With the defaults x [M, K], w [N, K], out [M, N] are 2-D row-strided tensors; the keyword
+           tile_group: Optional[torch.Tensor] = None, group_stride: int = 0, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = act(alpha * x @ w^T (+ bias)). With the defaults x [M, K], w [N, K], out [M, N] are 2-D row-strided tensors; the keyword
     overrides describe batched column slices (heads) or a grouped product over expert-sorted row tiles (see the header)."""
     _need_cuda(x, w, out, tile_group)
     M = x.shape[0] if M is None else M
@@ -92,8 +100,14 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, M: Optional[i
     ldx = x.stride(0) if ldx is None else ldx
     ldw = w.stride(-2) if ldw is None else ldw
     ldy = out.stride(0) if ldy is None else ldy
-    rc = load().omc_linear(_ptr(x), _dt(x), ldx, sx, _ptr(w), _dt(w), ldw, sw, _ptr(out), _dt(out), ldy, sy, M, N, K, batch,
-                           alpha, act, _ptr(tile_group), group_stride, _stream())
+    if bias is not None:
+        _need_cuda(bias)
+        assert bias.dtype == w.dtype and bias.numel() == N and batch == 1
+        rc = load().omc_linear_bias(_ptr(x), _dt(x), ldx, sx, _ptr(w), _dt(w), ldw, sw, _ptr(out), _dt(out), ldy, sy, M, N, K, batch,
+                                    alpha, act, _ptr(tile_group), group_stride, _ptr(bias), 0, _stream())
+    else:
+        rc = load().omc_linear(_ptr(x), _dt(x), ldx, sx, _ptr(w), _dt(w), ldw, sw, _ptr(out), _dt(out), ldy, sy, M, N, K, batch,
+                               alpha, act, _ptr(tile_group), group_stride, _stream())
     _check(rc, "omc_linear")
     return out
 
@@ -320,3 +334,106 @@ def moe_combine_norm(ys: Optional[torch.Tensor], slot_of, w, top: int, gate, ysh
                                      h32.stride(0), _ptr(xb), _dt(xb), xb.stride(0) if xb is not None else 0, h32.shape[0],
                                      h32.shape[1], _stream())
     _check(rc, "omc_moe_combine_norm")
+
+
+# ---- pre/post norms around sublayers, gated feed-forward halves
+def post_norm_residual(y1: torch.Tensor, w_post: torch.Tensor, eps: float, mult: float, h32: torch.Tensor,
+                       w_next: Optional[torch.Tensor], xb: Optional[torch.Tensor], y2: Optional[torch.Tensor] = None,
+                       wa: Optional[torch.Tensor] = None, wb: Optional[torch.Tensor] = None):
+    """h32 += mult * N(y), N(y) = y / rms(y) * (1 + w_post), with y = y1 or the mean of y1 / rms * wa and y2 / rms * wb;
+    xb = h32 / rms(h32) * (1 + w_next) (w_next None: the rounded h32)."""
+    _need_cuda(y1, y2, wa, wb, w_post, h32, w_next, xb)
+    assert y1.dtype == torch.float32 and h32.dtype == torch.float32 and y1.stride(1) == 1 and (y2 is None or y2.dtype == torch.float32)
+    rc = load().omc_post_norm_residual(_ptr(y1), y1.stride(0), _ptr(wa), _ptr(y2), y2.stride(0) if y2 is not None else 0, _ptr(wb),
+                                       _ptr(w_post), _dt(w_post), eps, mult, _ptr(h32), h32.stride(0), _ptr(w_next), _ptr(xb), _dt(xb),
+                                       xb.stride(0) if xb is not None else 0, h32.shape[0], h32.shape[1], _stream())
+    _check(rc, "omc_post_norm_residual")
+
+
+def glu_mul(z: torch.Tensor, n: int, act: int, out: torch.Tensor):
+    """out[:, c] = act(z[:, c]) * z[:, n + c]."""
+    _need_cuda(z, out)
+    assert z.dtype == torch.float32 and z.stride(1) == 1 and out.stride(1) == 1 and z.shape[1] >= 2 * n
+    rc = load().omc_glu_mul(_ptr(z), z.stride(0), z.shape[0], n, act, _ptr(out), _dt(out), out.stride(0), _stream())
+    _check(rc, "omc_glu_mul")
+    return out
+
+
+# ---- state mixers
+GATE_NONE, GATE_SILU, GATE_SIGMOID = 0, 1, 2
+DECAY_CONST, DECAY_HEAD, DECAY_CHANNEL = 0, 1, 2
+
+
+def causal_conv_silu(x: torch.Tensor, w: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor, state: Optional[torch.Tensor],
+                     y: torch.Tensor, unit_channels: int = 0, unit_group: int = 0, unit_eps: float = 1e-6, scaled_channels: int = 0,
+                     unit_mult: float = 1.0):
+    """x fp32 [T, >= ch] (a column slice is fine), w [ch, taps], state fp32 [slots, taps - 1, ch] -> y fp32 [T, ch]."""
+    _need_cuda(x, w, pos, slot, state, y)
+    ch, taps = w.shape
+    assert x.dtype == torch.float32 and y.dtype == torch.float32 and x.stride(1) == 1 and y.stride(1) == 1 and w.is_contiguous()
+    assert pos.dtype == torch.int32 and slot.dtype == torch.int32
+    assert taps == 1 or (state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (taps - 1, ch))
+    rc = load().omc_causal_conv_silu(_ptr(x), x.stride(0), x.shape[0], ch, _ptr(w), _dt(w), taps, _ptr(pos), _ptr(slot), _ptr(state),
+                                     _ptr(y), y.stride(0), unit_channels, unit_group, unit_eps, scaled_channels, unit_mult, _stream())
+    _check(rc, "omc_causal_conv_silu")
+    if taps > 1:
+        _core.add_launches(1)
+    return y
+
+
+def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, out: torch.Tensor, row_begin: torch.Tensor,
+                      portions: int, pos: torch.Tensor, slot: torch.Tensor, H: int, G: int, dim: int, vdim: int, *, silu_in: bool = False,
+                      decay_const: Optional[torch.Tensor] = None, a: Optional[torch.Tensor] = None, A_log: Optional[torch.Tensor] = None,
+                      dt_bias: Optional[torch.Tensor] = None, channel_decay: bool = False, beta: Optional[torch.Tensor] = None):
+    """The recurrence of omc_linear_state_scan; q / k / v / a / beta are fp32 2-D tensors or column slices of one."""
+    _need_cuda(q, k, v, state, out, row_begin, pos, slot, decay_const, a, A_log, dt_bias, beta)
+    for t in (q, k, v, out, a, beta):
+        assert t is None or (t.dtype == torch.float32 and t.stride(1) == 1)
+    for t in (decay_const, A_log, dt_bias):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, dim, vdim) and row_begin.dtype == torch.int32
+    mode = DECAY_CONST if decay_const is not None else (DECAY_CHANNEL if channel_decay else DECAY_HEAD)
+    rc = load().omc_linear_state_scan(_ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), 1 if silu_in else 0, mode,
+                                      _ptr(decay_const), _ptr(a), a.stride(0) if a is not None else 0, _ptr(A_log), _ptr(dt_bias),
+                                      _ptr(beta), beta.stride(0) if beta is not None else 0, _ptr(state), _ptr(out), out.stride(0),
+                                      _ptr(row_begin), portions, _ptr(pos), _ptr(slot), H, G, dim, vdim, _stream())
+    _check(rc, "omc_linear_state_scan")
+    return out
+
+
+def gated_rms_rows(x: torch.Tensor, groups: int, n: int, w: torch.Tensor, eps: float, gate: Optional[torch.Tensor], gate_act: int,
+                   out: torch.Tensor):
+    _need_cuda(x, w, gate, out)
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and out.stride(1) == 1 and w.numel() == n
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1)
+    rc = load().omc_gated_rms_rows(_ptr(x), x.stride(0), x.shape[0], groups, n, _ptr(w), _dt(w), eps, _ptr(gate),
+                                   gate.stride(0) if gate is not None else 0, gate_act, _ptr(out), _dt(out), out.stride(0), _stream())
+    _check(rc, "omc_gated_rms_rows")
+    return out
+
+
+# ---- windowed attention over a paged key/value cache
+def qk_norm_kv_store(q: torch.Tensor, wq: torch.Tensor, k: torch.Tensor, wk: torch.Tensor, v: torch.Tensor, eps: float, pos, slot,
+                     block_table: torch.Tensor, page_size: int, pool: torch.Tensor, q_out: torch.Tensor):
+    _need_cuda(q, wq, k, wk, v, pos, slot, block_table, pool, q_out)
+    nq, nk, nv = wq.numel(), wk.numel(), v.shape[1]
+    assert q.dtype == k.dtype == v.dtype == torch.float32 and q.stride(1) == k.stride(1) == v.stride(1) == 1
+    assert pool.is_contiguous() and pool.shape[-1] == nk + nv and pool.dtype == q_out.dtype and wq.dtype == wk.dtype
+    assert block_table.dtype == torch.int32 and block_table.is_contiguous() and q_out.stride(1) == 1
+    rc = load().omc_qk_norm_kv_store(_ptr(q), q.stride(0), nq, _ptr(wq), _ptr(k), k.stride(0), nk, _ptr(wk), _dt(wq), _ptr(v), v.stride(0),
+                                     nv, eps, q.shape[0], _ptr(pos), _ptr(slot), _ptr(block_table), block_table.shape[1], page_size,
+                                     _ptr(pool), _ptr(q_out), q_out.stride(0), _dt(pool), _stream())
+    _check(rc, "omc_qk_norm_kv_store")
+
+
+def window_attn(q: torch.Tensor, H: int, G: int, d: int, dv: int, pool: torch.Tensor, block_table: torch.Tensor, page_size: int, pos, slot,
+                window: int, scale: float, softcap: float, dist_bias: Optional[torch.Tensor], out: torch.Tensor):
+    """q [T, H * d] and pool of one dtype -> out [T, H * dv]."""
+    _need_cuda(q, pool, block_table, pos, slot, dist_bias, out)
+    assert q.dtype == pool.dtype and q.stride(1) == 1 and out.stride(1) == 1 and pool.is_contiguous() and pool.shape[-1] == G * (d + dv)
+    assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape == (window, H))
+    rc = load().omc_window_attn(_ptr(q), q.stride(0), q.shape[0], H, G, d, dv, _ptr(pool), _dt(pool), _ptr(block_table),
+                                block_table.shape[1], page_size, _ptr(pos), _ptr(slot), window, scale, softcap, _ptr(dist_bias), _ptr(out),
+                                _dt(out), out.stride(0), _stream())
+    _check(rc, "omc_window_attn")
+    return out
