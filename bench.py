@@ -297,6 +297,9 @@ def main():
     ap.add_argument("--voduzen", action="append", choices=["s", "m"], help="instead of the default workload: the Voduzen decoder "
                     "at this size (random weights) beside the Qwen2-MoE decoder at equal size - prefill and decode throughput "
                     "and the new kernels against their rooflines (tools/bench_voduzen.py); one JSON line per size")
+    ap.add_argument("--tifisun", action="append", choices=["s", "m"], help="instead of the default workload: the Tifisun decoder at "
+                    "this size (random weights) beside the dense Qwen2 decoder at equal size - prefill and decode throughput and "
+                    "the new kernels against their rooflines (tools/bench_tifisun.py); one JSON line per size")
     ap.add_argument("--pixel-shuffle", type=float, default=1.0, help="mm_pixel_shuffle_ratio (1.0 = reference behaviour)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -308,6 +311,14 @@ def main():
         torch.cuda.set_device(0)
         for size in args.voduzen:
             print(json.dumps(measure_voduzen(size, steps=max(args.steps, 8))), flush=True)
+        return
+
+    if args.tifisun:
+        import torch
+        from tools.bench_tifisun import measure as measure_tifisun
+        torch.cuda.set_device(0)
+        for size in args.tifisun:
+            print(json.dumps(measure_tifisun(size, steps=max(args.steps, 8))), flush=True)
         return
 
     import torch

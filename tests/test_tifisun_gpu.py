@@ -168,7 +168,9 @@ def test_linear_state_scan_against_token_loop(dim, vdim, H, G, mode):
     g = torch.Generator().manual_seed(dim + vdim)
     T = 37
     q = torch.randn(T, G * dim, generator=g, dtype=F64) * 0.5
-    k = torch.randn(T, G * dim, generator=g, dtype=F64) * 0.5
+    k = torch.randn(T, G * dim, generator=g, dtype=F64)
+    if mode != "const":     # the delta rule is a contraction only for keys of at most unit length (the model feeds it unit vectors)
+        k = O.unit_vectors(k, G)
     v = torch.randn(T, H * vdim, generator=g, dtype=F64)
     A_log = torch.randn(H, generator=g, dtype=F64) - 1.5
     a = torch.randn(T, H * dim if mode == "channel" else H, generator=g, dtype=F64)
@@ -300,12 +302,14 @@ def test_window_edge_key_dominates_or_is_unseen(edge, decoded):
     j = i - window + 1 if edge == "inside" else i - window
     e = torch.zeros(d, dtype=F64)
     e[3] = 1.0
-    k[j] = e * 4.0                # after the norm over d: one large component
-    q[i] = torch.cat([e, e]) * 4.0
+    k[:, 3] = 0.0                 # every other key is orthogonal to the query: score 0
+    k[j] = e
+    q[i] = torch.cat([e, e])      # after the norms: one component of 4 in the query's heads and in that key; the weight makes it 20
     rel = torch.zeros(10, H, dtype=F64)
     cuts = [0, T - 1, T] if decoded else [0, T]
-    got = _window_case(H, G, d, dv, window, page, 1000.0, torch.float32, q, k, v, rel, 40.0, cuts)
-    want = O.windowed_attention(O.norm_plain(q, torch.ones(H * d, dtype=F64), 1e-5), O.norm_plain(k, torch.ones(d, dtype=F64), 1e-5), v, H, G,
+    wq = torch.full((H * d,), 5.0, dtype=F64)
+    got = _window_case(H, G, d, dv, window, page, 1000.0, torch.float32, q, k, v, rel, 40.0, cuts, wq=wq)
+    want = O.windowed_attention(O.norm_plain(q, wq, 1e-5), O.norm_plain(k, torch.ones(d, dtype=F64), 1e-5), v, H, G,
                                 d ** -0.5, 1000.0, rel, 40.0, window)
     assert torch.allclose(got[i], want[i], atol=1e-4)
     if edge == "inside":
@@ -459,7 +463,7 @@ def test_far_tokens_stay_in_the_state_and_long_decoding(dtype):
     # the far token matters: the reference itself changes when token 5 changes
     changed = list(toks)
     changed[5] = (changed[5] + 1) % cd["vocab"]
-    assert rel_err(oracle_logits(cd, sd, changed)[-1:], want[-1:]) > 20 * TOL[dtype]
+    assert rel_err(oracle_logits(cd, sd, changed)[-1:], want[-1:]) > 100 * TOL[torch.float32]     # far above what float32 is held to
     steps, at = [], 0
     for n in (100, 61, 2, 97):
         steps.append(([("m", toks[at:at + n], [n - 1]), ("o", other[at:at + n], [])], []))
