@@ -187,6 +187,15 @@ int omc_window_attn(const void* q, long long ldq, int T, int H, int G, int d, in
                     const int32_t* block_table, int max_pages, int page_size, const int32_t* pos, const int32_t* slot, int window,
                     float scale, float softcap, const float* dist_bias, void* out, int out_dt, long long ldo, void* stream);
 
+/* Tensor-core version of omc_window_attn (bf16 q and pool; d and dv multiples of 16, d <= 256, dv <= 128, H / G a divisor of 64 -
+ * omc_window_attn_mma_ok says 1). items: int32 [n_items][4] (first_row, n_tok, slot, first_pos), n_tok <= 64 / (H / G) consecutive
+ * rows of one request; items NULL: every one of the T rows is an item of its own, taken from pos / slot on the device. Same
+ * results as omc_window_attn up to the bf16 rounding of the probabilities and the hardware tanh of the soft cap. */
+int omc_window_attn_mma_ok(int H, int G, int d, int dv);
+int omc_window_attn_mma(const void* q, long long ldq, int T, int H, int G, int d, int dv, const void* pool, const int32_t* block_table,
+                        int max_pages, int page_size, const int32_t* items, int n_items, const int32_t* pos, const int32_t* slot,
+                        int window, float scale, float softcap, const float* dist_bias, void* out, int out_dt, long long ldo, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

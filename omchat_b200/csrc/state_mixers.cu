@@ -10,9 +10,9 @@
 // The recurrence is evaluated token by token in every case - prompt portions and single decoded tokens run the same
 // instructions in the same order, which makes the result independent of how a prompt is cut. Its parallelism is over the
 // independent COLUMNS of S: column j of a head's state only ever meets v[:, j], so a CTA owns 32 columns of one head of one
-// portion, four lanes share a column (each holds dim / 4 state elements in registers) and finish the two dot products of a
-// token with two shuffles each. Tokens are staged 16 at a time in shared memory (decays, sigmoid and unit scaling applied on
-// the way in), so the sequential loop touches registers and shared memory only.
+// portion, four lanes share a column (each holds a quarter of its state elements in registers) and finish the two dot products of
+// a token with two shuffles each. Tokens are staged 16 at a time in shared memory by cp.async, one chunk ahead of the one being
+// computed (decays, sigmoid and silu applied in place on arrival), so the sequential loop touches registers and shared memory only.
 #include "seq_common.cuh"
 
 namespace omc {
@@ -100,108 +100,167 @@ struct ScanArgs {
   int H, G, dim, vdim;
 };
 
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src));
+}
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src));
+}
+
+// Shared-memory place of key channel i: lane l = i / DPT owns DPT consecutive channels (read as float4), and a gap of four floats
+// between the lanes' blocks moves them to different banks.
 template <int DPT>
+__device__ __forceinline__ int scan_place(int i) { return (i / DPT) * (DPT + 4) + (i % DPT); }
+
+// Two stages of kScanTok tokens each: the raw inputs of the next chunk arrive by cp.async while the current chunk is computed;
+// after arrival one pass turns them in place into what the recurrence uses (silu, decays, sigmoid). VEC: 16-byte copies
+// (every row starts on a 16-byte boundary and the widths are multiples of four), else 4-byte copies.
+template <int DPT, bool VEC>
 __global__ void __launch_bounds__(kScanCols * kScanLanes) linear_state_scan_kernel(ScanArgs a) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
+  constexpr int PITCH = kScanLanes * (DPT + 4);
   const int dim = a.dim;
-  float* sk = sm;                          // [tok][dim]
-  float* sq = sk + kScanTok * dim;         // [tok][dim]
-  float* sg = sq + kScanTok * dim;         // [tok][dim] (mode 2) or [tok]
-  const int gw = a.decay_mode == 2 ? dim : 1;
-  float* sv = sg + kScanTok * gw;          // [tok][cols]
-  float* sb = sv + kScanTok * kScanCols;   // [tok]
+  const bool chan = a.decay_mode == 2;
+  const int stage_floats = kScanTok * PITCH * (chan ? 3 : 2) + kScanTok * kScanCols + 2 * kScanTok;
   const int h = blockIdx.y, kvh = h / (a.H / a.G);
   const int col0 = blockIdx.x * kScanCols;
   const int r0 = a.row_begin[blockIdx.z], r1 = a.row_begin[blockIdx.z + 1];
   if (r1 <= r0) return;
   const int tid = threadIdx.x, lane = tid & (kScanLanes - 1), col = col0 + (tid >> 2);
   const bool col_ok = col < a.vdim;
+  for (int e = tid; e < 2 * stage_floats; e += blockDim.x) sm[e] = 0.f;   // the pads stay zero: they meet zero state only
   float* S = a.state + (((long long)a.slot[r0] * a.H + h) * dim) * a.vdim;
   float st[DPT];
   const bool fresh = a.pos[r0] == 0;
 #pragma unroll
   for (int r = 0; r < DPT; ++r) {
-    const int i = lane + kScanLanes * r;
+    const int i = lane * DPT + r;
     st[r] = (!fresh && col_ok && i < dim) ? S[(long long)i * a.vdim + col] : 0.f;
   }
   const float A = a.decay_mode != 0 ? expf(a.A_log[h]) : 0.f;
   const float gconst = a.decay_mode == 0 ? a.decay_const[h] : 1.f;
-  for (int c0 = r0; c0 < r1; c0 += kScanTok) {
-    const int n = min(kScanTok, r1 - c0);
-    __syncthreads();
-    for (int e = tid; e < n * dim; e += blockDim.x) {
-      const int tt = e / dim, i = e - tt * dim;
-      float kv = a.k[(long long)(c0 + tt) * a.ldk + kvh * dim + i], qv = a.q[(long long)(c0 + tt) * a.ldq + kvh * dim + i];
-      if (a.silu_in) {
-        kv = silu_f(kv);
-        qv = silu_f(qv);
+  __syncthreads();
+
+  auto issue = [&](int c0, int n, int stage) {
+    float* sk = sm + stage * stage_floats;
+    float* sq = sk + kScanTok * PITCH;
+    float* sg = sq + kScanTok * PITCH;                       // [tok][PITCH] (per channel) or [tok]
+    float* sv = sg + (chan ? kScanTok * PITCH : kScanTok);
+    float* sb = sv + kScanTok * kScanCols;
+    if (VEC) {
+      const int d4 = dim >> 2;
+      for (int e = tid; e < n * d4; e += blockDim.x) {
+        const int tt = e / d4, i = (e - tt * d4) << 2, at = tt * PITCH + scan_place<DPT>(i);
+        cp_async16(sk + at, a.k + (long long)(c0 + tt) * a.ldk + kvh * dim + i);
+        cp_async16(sq + at, a.q + (long long)(c0 + tt) * a.ldq + kvh * dim + i);
+        if (chan) cp_async16(sg + at, a.a + (long long)(c0 + tt) * a.lda + h * dim + i);
       }
-      sk[tt * dim + i] = kv;
-      sq[tt * dim + i] = qv;
-      if (a.decay_mode == 2)
-        sg[tt * dim + i] = expf(-A * softplus_f(a.a[(long long)(c0 + tt) * a.lda + h * dim + i] + a.dt_bias[h * dim + i]));
-    }
-    for (int e = tid; e < n * kScanCols; e += blockDim.x) {
-      const int tt = e / kScanCols, j = e - tt * kScanCols;
-      float vv = col0 + j < a.vdim ? a.v[(long long)(c0 + tt) * a.ldv + h * a.vdim + col0 + j] : 0.f;
-      if (a.silu_in) vv = silu_f(vv);
-      sv[e] = vv;
+      for (int e = tid; e < n * (kScanCols / 4); e += blockDim.x) {
+        const int tt = e / (kScanCols / 4), j = (e - tt * (kScanCols / 4)) << 2;
+        if (col0 + j < a.vdim) cp_async16(sv + tt * kScanCols + j, a.v + (long long)(c0 + tt) * a.ldv + h * a.vdim + col0 + j);
+      }
+    } else {
+      for (int e = tid; e < n * dim; e += blockDim.x) {
+        const int tt = e / dim, i = e - tt * dim, at = tt * PITCH + scan_place<DPT>(i);
+        cp_async4(sk + at, a.k + (long long)(c0 + tt) * a.ldk + kvh * dim + i);
+        cp_async4(sq + at, a.q + (long long)(c0 + tt) * a.ldq + kvh * dim + i);
+        if (chan) cp_async4(sg + at, a.a + (long long)(c0 + tt) * a.lda + h * dim + i);
+      }
+      for (int e = tid; e < n * kScanCols; e += blockDim.x) {
+        const int tt = e / kScanCols, j = e - tt * kScanCols;
+        if (col0 + j < a.vdim) cp_async4(sv + e, a.v + (long long)(c0 + tt) * a.ldv + h * a.vdim + col0 + j);
+      }
     }
     if (tid < n) {
-      sb[tid] = a.beta != nullptr ? sigmoid_f(a.beta[(long long)(c0 + tid) * a.ldb + h]) : 1.f;
-      if (a.decay_mode == 1) sg[tid] = expf(-A * softplus_f(a.a[(long long)(c0 + tid) * a.lda + h] + a.dt_bias[h]));
+      if (a.beta != nullptr) cp_async4(sb + tid, a.beta + (long long)(c0 + tid) * a.ldb + h);
+      if (a.decay_mode == 1) cp_async4(sg + tid, a.a + (long long)(c0 + tid) * a.lda + h);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  issue(r0, min(kScanTok, r1 - r0), 0);
+  int stage = 0;
+  for (int c0 = r0; c0 < r1; c0 += kScanTok, stage ^= 1) {
+    const int n = min(kScanTok, r1 - c0);
+    if (c0 + kScanTok < r1) {
+      issue(c0 + kScanTok, min(kScanTok, r1 - c0 - kScanTok), stage ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    float* sk = sm + stage * stage_floats;
+    float* sq = sk + kScanTok * PITCH;
+    float* sg = sq + kScanTok * PITCH;
+    float* sv = sg + (chan ? kScanTok * PITCH : kScanTok);
+    float* sb = sv + kScanTok * kScanCols;
+    // raw inputs -> what the recurrence uses
+    if (a.silu_in || chan) {
+      for (int e = tid; e < n * dim; e += blockDim.x) {
+        const int tt = e / dim, i = e - tt * dim, at = tt * PITCH + scan_place<DPT>(i);
+        if (a.silu_in) {
+          sk[at] = silu_f(sk[at]);
+          sq[at] = silu_f(sq[at]);
+        }
+        if (chan) sg[at] = expf(-A * softplus_f(sg[at] + a.dt_bias[h * dim + i]));
+      }
+    }
+    if (a.silu_in)
+      for (int e = tid; e < n * kScanCols; e += blockDim.x) sv[e] = silu_f(sv[e]);
+    if (tid < n) {
+      sb[tid] = a.beta != nullptr ? sigmoid_f(sb[tid]) : 1.f;
+      if (a.decay_mode == 1) sg[tid] = expf(-A * softplus_f(sg[tid] + a.dt_bias[h]));
       else if (a.decay_mode == 0) sg[tid] = gconst;
     }
     __syncthreads();
     for (int tt = 0; tt < n; ++tt) {
-      const float* kr = sk + tt * dim;
-      const float* qr = sq + tt * dim;
-      float dot = 0.f;
-      if (a.decay_mode == 2) {
-        const float* gr = sg + tt * dim;
+      const float* kr = sk + tt * PITCH + lane * (DPT + 4);
+      const float* qr = sq + tt * PITCH + lane * (DPT + 4);
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+      if (chan) {
+        const float* gr = sg + tt * PITCH + lane * (DPT + 4);
 #pragma unroll
-        for (int r = 0; r < DPT; ++r) {
-          const int i = lane + kScanLanes * r;
-          if (i < dim) {
-            st[r] *= gr[i];
-            dot = fmaf(st[r], kr[i], dot);
-          }
+        for (int r = 0; r < DPT; r += 4) {
+          const float4 kv = *reinterpret_cast<const float4*>(kr + r);
+          const float4 gv = *reinterpret_cast<const float4*>(gr + r);
+          st[r] *= gv.x, st[r + 1] *= gv.y, st[r + 2] *= gv.z, st[r + 3] *= gv.w;
+          d0 = fmaf(st[r], kv.x, d0), d1 = fmaf(st[r + 1], kv.y, d1), d2 = fmaf(st[r + 2], kv.z, d2), d3 = fmaf(st[r + 3], kv.w, d3);
         }
       } else {
         const float g = sg[tt];
 #pragma unroll
-        for (int r = 0; r < DPT; ++r) {
-          const int i = lane + kScanLanes * r;
-          if (i < dim) {
-            st[r] *= g;
-            dot = fmaf(st[r], kr[i], dot);
-          }
+        for (int r = 0; r < DPT; r += 4) {
+          const float4 kv = *reinterpret_cast<const float4*>(kr + r);
+          st[r] *= g, st[r + 1] *= g, st[r + 2] *= g, st[r + 3] *= g;
+          d0 = fmaf(st[r], kv.x, d0), d1 = fmaf(st[r + 1], kv.y, d1), d2 = fmaf(st[r + 2], kv.z, d2), d3 = fmaf(st[r + 3], kv.w, d3);
         }
       }
       float u = sv[tt * kScanCols + (tid >> 2)];
       if (a.beta != nullptr) {
+        float dot = (d0 + d1) + (d2 + d3);
         dot += __shfl_xor_sync(0xffffffffu, dot, 1);
         dot += __shfl_xor_sync(0xffffffffu, dot, 2);
         u = sb[tt] * (u - dot);
       }
-      float o = 0.f;
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-      for (int r = 0; r < DPT; ++r) {
-        const int i = lane + kScanLanes * r;
-        if (i < dim) {
-          st[r] = fmaf(kr[i], u, st[r]);
-          o = fmaf(st[r], qr[i], o);
-        }
+      for (int r = 0; r < DPT; r += 4) {
+        const float4 kv = *reinterpret_cast<const float4*>(kr + r);
+        const float4 qv = *reinterpret_cast<const float4*>(qr + r);
+        st[r] = fmaf(kv.x, u, st[r]), st[r + 1] = fmaf(kv.y, u, st[r + 1]), st[r + 2] = fmaf(kv.z, u, st[r + 2]), st[r + 3] = fmaf(kv.w, u, st[r + 3]);
+        o0 = fmaf(st[r], qv.x, o0), o1 = fmaf(st[r + 1], qv.y, o1), o2 = fmaf(st[r + 2], qv.z, o2), o3 = fmaf(st[r + 3], qv.w, o3);
       }
+      float o = (o0 + o1) + (o2 + o3);
       o += __shfl_xor_sync(0xffffffffu, o, 1);
       o += __shfl_xor_sync(0xffffffffu, o, 2);
       if (lane == 0 && col_ok) a.out[(long long)(c0 + tt) * a.ldo + h * a.vdim + col] = o;
     }
+    __syncthreads();   // the next iteration's copies overwrite the stage that was just read
   }
   if (col_ok) {
 #pragma unroll
     for (int r = 0; r < DPT; ++r) {
-      const int i = lane + kScanLanes * r;
+      const int i = lane * DPT + r;
       if (i < dim) S[(long long)i * a.vdim + col] = st[r];
     }
   }
@@ -271,20 +330,34 @@ extern "C" int omc_linear_state_scan(const float* q, long long ldq, const float*
   ScanArgs s{q, k, v, ldq, ldk, ldv, silu_in, decay_mode, decay_const, a, lda, A_log, dt_bias, beta, ldb, state, out, ldo,
              row_begin, pos, slot, H, G, dim, vdim};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const size_t smem = sizeof(float) * ((size_t)kScanTok * dim * 2 + (size_t)kScanTok * (decay_mode == 2 ? dim : 1) + kScanTok * kScanCols + kScanTok);
+  const int dpt = dim <= 32 ? 8 : (dim <= 64 ? 16 : (dim <= 128 ? 32 : 64));
+  const size_t stage_floats = (size_t)kScanTok * kScanLanes * (dpt + 4) * (decay_mode == 2 ? 3 : 2) + kScanTok * kScanCols + 2 * kScanTok;
+  const size_t smem = 2 * stage_floats * sizeof(float);
   dim3 grid((vdim + kScanCols - 1) / kScanCols, H, portions);
   const int threads = kScanCols * kScanLanes;
-  if (dim <= 32) linear_state_scan_kernel<8><<<grid, threads, smem, st>>>(s);
-  else if (dim <= 64) linear_state_scan_kernel<16><<<grid, threads, smem, st>>>(s);
-  else if (dim <= 128) linear_state_scan_kernel<32><<<grid, threads, smem, st>>>(s);
-  else {
-    static bool attr_done[kMaxDevices] = {};
-    if (smem > 48 * 1024 && !attr_done[cur_device()]) {
-      cudaFuncSetAttribute(linear_state_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-      attr_done[cur_device()] = true;
-    }
-    linear_state_scan_kernel<64><<<grid, threads, smem, st>>>(s);
-  }
+  auto al16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const bool vec = dim % 4 == 0 && vdim % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ldv % 4 == 0 && al16(q) && al16(k) && al16(v) &&
+                   (decay_mode != 2 || (lda % 4 == 0 && al16(a)));
+#define OMC_SCAN_LAUNCH(DPT, VEC)                                                                                        \
+  do {                                                                                                                   \
+    static bool attr_done[kMaxDevices] = {};                                                                             \
+    if (!attr_done[cur_device()]) {                                                                                      \
+      cudaFuncSetAttribute(linear_state_scan_kernel<DPT, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024); \
+      attr_done[cur_device()] = true;                                                                                    \
+    }                                                                                                                    \
+    linear_state_scan_kernel<DPT, VEC><<<grid, threads, smem, st>>>(s);                                                  \
+  } while (0)
+#define OMC_SCAN_DPT(DPT)          \
+  do {                             \
+    if (vec) OMC_SCAN_LAUNCH(DPT, true); \
+    else OMC_SCAN_LAUNCH(DPT, false);    \
+  } while (0)
+  if (dpt == 8) OMC_SCAN_DPT(8);
+  else if (dpt == 16) OMC_SCAN_DPT(16);
+  else if (dpt == 32) OMC_SCAN_DPT(32);
+  else OMC_SCAN_DPT(64);
+#undef OMC_SCAN_DPT
+#undef OMC_SCAN_LAUNCH
   return check_launch("omc_linear_state_scan");
 }
 

@@ -124,6 +124,228 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(const TQ* _
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Tensor-core kernel (bf16; head widths multiples of 16, values up to 128 wide, heads per key/value head a divisor of 64).
+// mma.sync.m16n8k16 over 64-key tiles staged by cp.async straight out of the pages, two buffers. The 64 rows of a tile are
+// (token, query head) pairs of ONE key/value head - 64 / (H / G) consecutive tokens of one request - so the heads of a group share
+// the staged keys and values. Four warps of 16 rows; S = Q K^T, then scale, soft cap (tanh.approx), distance bias and window
+// mask on the accumulators, online softmax in base 2, P (bf16, from the accumulator registers) times V through ldmatrix.trans.
+// Work items: int32[4] (first_row, n_tok, slot, first_pos) from the host, or - items == NULL - every row an item of its own,
+// read from pos / slot on the device (decode steps, replayable from a CUDA graph).
+__device__ __forceinline__ uint32_t wsmem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void w_ldsm_x4(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr));
+}
+__device__ __forceinline__ void w_ldsm_x4_t(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr));
+}
+__device__ __forceinline__ void w_mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void w_cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t w_pack2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void w_st_pair(float* p, float x, float y) { *reinterpret_cast<float2*>(p) = make_float2(x, y); }
+__device__ __forceinline__ void w_st_pair(bf16_t* p, float x, float y) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(x, y); }
+
+constexpr int kWmRows = 64, kWmKeys = 64;
+
+struct WinMmaArgs {
+  const bf16_t* q;
+  long long ldq;
+  const bf16_t* pool;
+  const int32_t* bt;
+  const int32_t* items;   // [n][4] or NULL
+  const int32_t* pos;
+  const int32_t* slot;
+  const float* bias;      // [window][H] or NULL
+  void* out;
+  long long ldo;
+  int max_pages, page_size, H, G, d, dv, window;
+  float scale, softcap;
+};
+
+template <int NV, typename TO>  // NV: 8-column output tiles, dv <= 8 * NV
+__global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
+  extern __shared__ __align__(16) unsigned char wsm_raw[];
+  const int d = a.d, dv = a.dv, pq = d + 8, pv = dv + 8;
+  bf16_t* Qs = reinterpret_cast<bf16_t*>(wsm_raw);
+  bf16_t* Ks = Qs + kWmRows * pq;          // [2][64][pq]
+  bf16_t* Vs = Ks + 2 * kWmKeys * pq;      // [2][64][pv]
+  int first_row, n_tok, slot, first_pos;
+  if (a.items != nullptr) {
+    const int32_t* it = a.items + blockIdx.x * 4;
+    first_row = it[0], n_tok = it[1], slot = it[2], first_pos = it[3];
+  } else {
+    first_row = blockIdx.x, n_tok = 1, slot = a.slot[blockIdx.x], first_pos = a.pos[blockIdx.x];
+  }
+  const int kvh = blockIdx.y, rep = a.H / a.G;
+  const int n_rows = n_tok * rep;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int qchunks = d >> 3, vchunks = dv >> 3;
+  for (int i = tid; i < kWmRows * qchunks; i += blockDim.x) {
+    const int row = i / qchunks, c = i - row * qchunks;
+    bf16_t* dst = Qs + row * pq + c * 8;
+    if (row < n_rows) w_cp_async16(wsmem_u32(dst), a.q + (long long)(first_row + row / rep) * a.ldq + (kvh * rep + row % rep) * d + c * 8);
+    else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+  }
+  const int row0 = warp * 16 + g, row1 = row0 + 8;
+  const int p0 = row0 < n_rows ? first_pos + row0 / rep : -1, p1 = row1 < n_rows ? first_pos + row1 / rep : -1;   // -1: no such row
+  const int h0 = kvh * rep + row0 % rep, h1 = kvh * rep + row1 % rep;
+  const int32_t* bt = a.bt + (long long)slot * a.max_pages;
+  const int k_begin = max(0, first_pos - a.window + 1), k_end = first_pos + n_tok;
+  const int roww = a.G * (d + dv);
+  auto stage = [&](int buf, int j0) {
+    bf16_t* kb = Ks + buf * kWmKeys * pq;
+    bf16_t* vb = Vs + buf * kWmKeys * pv;
+    for (int i = tid; i < kWmKeys * (qchunks + vchunks); i += blockDim.x) {
+      const int key = i / (qchunks + vchunks), c = i - key * (qchunks + vchunks);
+      const int j = j0 + key;
+      bf16_t* dst = c < qchunks ? kb + key * pq + c * 8 : vb + key * pv + (c - qchunks) * 8;
+      if (j < k_end) {
+        const bf16_t* row = a.pool + ((long long)bt[j / a.page_size] * a.page_size + j % a.page_size) * roww;
+        w_cp_async16(wsmem_u32(dst), c < qchunks ? row + kvh * d + c * 8 : row + a.G * d + kvh * dv + (c - qchunks) * 8);
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[NV][4];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  const int nv = dv >> 3;
+  constexpr float kLog2e = 1.4426950408889634f;
+  const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
+  stage(0, k_begin);
+  int kt = 0;
+  for (int j0 = k_begin; j0 < k_end; j0 += kWmKeys, ++kt) {
+    const int buf = kt & 1;
+    if (j0 + kWmKeys < k_end) {
+      stage(buf ^ 1, j0 + kWmKeys);   // released by the barrier that ended the previous tile
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp * 16 < n_rows) {   // a warp without rows (decode: H / G of the 64 rows) only helps staging
+      const bf16_t* Kc = Ks + buf * kWmKeys * pq;
+      const bf16_t* Vc = Vs + buf * kWmKeys * pv;
+      float s[8][4];
+#pragma unroll
+      for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+      const uint32_t q_base = wsmem_u32(Qs + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * pq + 8 * (lane >> 4));
+      const uint32_t k_base = wsmem_u32(Kc + ((lane & 7) + 8 * (lane >> 4)) * pq + 8 * ((lane >> 3) & 1));
+      for (int kk = 0; kk < d; kk += 16) {
+        uint32_t a0, a1, a2, a3;
+        w_ldsm_x4(q_base + kk * 2, a0, a1, a2, a3);
+#pragma unroll
+        for (int n2 = 0; n2 < 4; ++n2) {
+          uint32_t b0, b1, b2, b3;
+          w_ldsm_x4(k_base + (n2 * 16 * pq + kk) * 2, b0, b1, b2, b3);
+          w_mma_bf16(s[2 * n2], a0, a1, a2, a3, b0, b1);
+          w_mma_bf16(s[2 * n2 + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+      // scale, soft cap, distance bias, window: scores in base-2 units
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = j0 + n * 8 + 2 * t4 + (e & 1);
+          const int p = e < 2 ? p0 : p1, hh = e < 2 ? h0 : h1;
+          const int dist = p - key;
+          float v = -INFINITY;
+          if (dist >= 0 && dist < a.window) {
+            v = s[n][e] * a.scale;
+            if (a.softcap > 0.f) v = a.softcap * tanh_approx(v * inv_cap);
+            if (a.bias != nullptr) v += __ldg(a.bias + (long long)dist * a.H + hh);
+            v *= kLog2e;
+          }
+          s[n][e] = v;
+        }
+        mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+        mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;   // rows that see nothing yet
+      const float c0 = exp2f(m0 - ms0), c1 = exp2f(m1 - ms1);
+      m0 = mn0;
+      m1 = mn1;
+      float rs0 = 0.f, rs1 = 0.f;
+      uint32_t p[8][2];
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        p[n][0] = w_pack2(exp2f(s[n][0] - ms0), exp2f(s[n][1] - ms0));
+        p[n][1] = w_pack2(exp2f(s[n][2] - ms1), exp2f(s[n][3] - ms1));
+        // the denominator sums the ROUNDED probabilities, the ones the numerator uses
+        const float2 f0 = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&p[n][0]));
+        const float2 f1 = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&p[n][1]));
+        rs0 += f0.x + f0.y;
+        rs1 += f1.x + f1.y;
+      }
+      l0 = l0 * c0 + rs0;
+      l1 = l1 * c1 + rs1;
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        o[j][0] *= c0;
+        o[j][1] *= c0;
+        o[j][2] *= c1;
+        o[j][3] *= c1;
+      }
+      const uint32_t v_base = wsmem_u32(Vc + ((lane & 7) + 8 * ((lane >> 3) & 1)) * pv + 8 * (lane >> 4));
+#pragma unroll
+      for (int kb16 = 0; kb16 < 4; ++kb16) {
+        const uint32_t a0 = p[2 * kb16][0], a1 = p[2 * kb16][1], a2 = p[2 * kb16 + 1][0], a3 = p[2 * kb16 + 1][1];
+#pragma unroll
+        for (int j = 0; j < NV; j += 2) {
+          if (j < nv) {   // dv is a multiple of 16: tiles come in pairs
+            uint32_t b0, b1, b2, b3;
+            w_ldsm_x4_t(v_base + (kb16 * 16 * pv + j * 8) * 2, b0, b1, b2, b3);
+            w_mma_bf16(o[j], a0, a1, a2, a3, b0, b1);
+            w_mma_bf16(o[j + 1], a0, a1, a2, a3, b2, b3);
+          }
+        }
+      }
+    }
+    __syncthreads();   // every warp is done with this tile's buffers
+  }
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float i0 = 1.f / l0, i1 = 1.f / l1;
+  TO* out0 = static_cast<TO*>(a.out) + (long long)(first_row + row0 / rep) * a.ldo + h0 * dv;
+  TO* out1 = static_cast<TO*>(a.out) + (long long)(first_row + row1 / rep) * a.ldo + h1 * dv;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    if (j < nv) {
+      const int col = j * 8 + 2 * t4;
+      if (row0 < n_rows) w_st_pair(out0 + col, o[j][0] * i0, o[j][1] * i0);
+      if (row1 < n_rows) w_st_pair(out1 + col, o[j][2] * i1, o[j][3] * i1);
+    }
+  }
+}
+
 }  // namespace omc
 
 using namespace omc;
@@ -165,4 +387,49 @@ extern "C" int omc_window_attn(const void* q, long long ldq, int T, int H, int G
                                                                             static_cast<TY*>(out), ldo);
   }))
   return check_launch("omc_window_attn");
+}
+
+extern "C" int omc_window_attn_mma_ok(int H, int G, int d, int dv) {
+  if (H <= 0 || G <= 0 || H % G) return 0;
+  const int rep = H / G;
+  return (d % 16 == 0 && dv % 16 == 0 && d >= 16 && d <= 256 && dv >= 16 && dv <= 128 && rep <= 64 && 64 % rep == 0) ? 1 : 0;
+}
+
+extern "C" int omc_window_attn_mma(const void* q, long long ldq, int T, int H, int G, int d, int dv, const void* pool,
+                                   const int32_t* block_table, int max_pages, int page_size, const int32_t* items, int n_items,
+                                   const int32_t* pos, const int32_t* slot, int window, float scale, float softcap,
+                                   const float* dist_bias, void* out, int out_dt, long long ldo, void* stream) {
+  if (q == nullptr || pool == nullptr || block_table == nullptr || out == nullptr || T < 0 || window < 1 || page_size <= 0 ||
+      max_pages <= 0 || (items == nullptr && (pos == nullptr || slot == nullptr)) || n_items < 0)
+    return set_error(OMC_ERR_ARG, "omc_window_attn_mma: bad argument");
+  if (!omc_window_attn_mma_ok(H, G, d, dv) || ldq % 8 || ldo % 2 || reinterpret_cast<uintptr_t>(q) % 16 || reinterpret_cast<uintptr_t>(pool) % 16)
+    return set_error(OMC_ERR_SHAPE, "omc_window_attn_mma: shape or alignment not supported (see omc_window_attn_mma_ok)");
+  const int n = items != nullptr ? n_items : T;
+  if (n == 0) return OMC_OK;
+  if (G > 65535) return set_error(OMC_ERR_SHAPE, "omc_window_attn_mma: more than 65535 key/value heads");
+  WinMmaArgs a{static_cast<const bf16_t*>(q), ldq, static_cast<const bf16_t*>(pool), block_table, items, pos, slot, dist_bias, out, ldo,
+               max_pages, page_size, H, G, d, dv, window, scale, softcap};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t smem = sizeof(bf16_t) * ((size_t)kWmRows * (d + 8) + 2 * (size_t)kWmKeys * (d + 8) + 2 * (size_t)kWmKeys * (dv + 8));
+  dim3 grid(n, G);
+#define OMC_WIN_LAUNCH(NV, TO)                                                                                      \
+  do {                                                                                                              \
+    static bool attr_done[kMaxDevices] = {};                                                                        \
+    if (!attr_done[cur_device()]) {                                                                                 \
+      cudaFuncSetAttribute(window_attn_mma_kernel<NV, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+      attr_done[cur_device()] = true;                                                                               \
+    }                                                                                                               \
+    window_attn_mma_kernel<NV, TO><<<grid, 128, smem, st>>>(a);                                                     \
+  } while (0)
+  if (out_dt == OMC_DT_BF16) {
+    if (dv <= 64) OMC_WIN_LAUNCH(8, bf16_t);
+    else OMC_WIN_LAUNCH(16, bf16_t);
+  } else if (out_dt == OMC_DT_F32) {
+    if (dv <= 64) OMC_WIN_LAUNCH(8, float);
+    else OMC_WIN_LAUNCH(16, float);
+  } else {
+    return set_error(OMC_ERR_ARG, "omc_window_attn_mma: unknown output dtype");
+  }
+#undef OMC_WIN_LAUNCH
+  return check_launch("omc_window_attn_mma");
 }

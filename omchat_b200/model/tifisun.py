@@ -252,6 +252,7 @@ class TifisunDecoder:
         self._graphs = {}         # (rows, id(cache)) -> captured decode-only step
         self._arange = None       # int32 [n + 1]: portion starts of a step whose rows are one request each
         self.use_graph = True
+        self.tensor_attention = True    # False: the plain attention kernel for every shape (A/B, tests)
 
     # ---- cache
     def cache_widths(self) -> List[int]:
@@ -302,7 +303,7 @@ class TifisunDecoder:
         seqlib.gated_rms_rows(o, H, dv, mw.norm, self.eps, gate, seqlib.GATE_SIGMOID if m.channel_decay else seqlib.GATE_SILU, on)
         return self._linear(on, mw.o, f32)
 
-    def _parallel(self, li: int, xb, pos, slot, cache: PagedStateCache, row_begin, n_portions: int):
+    def _parallel(self, li: int, xb, pos, slot, cache: PagedStateCache, row_begin, n_portions: int, plans: Optional[dict] = None):
         m: ParallelMixerSpec = self.cfg.layers[li].mixer
         mw: ParallelW = self.w.layers[li].mix
         L, R = m.left, m.right
@@ -315,8 +316,19 @@ class TifisunDecoder:
         seqlib.qk_norm_kv_store(z[:, c["lq"]], mw.q_norm, z[:, c["lk"]], mw.k_norm, z[:, c["lv"]], self.eps, pos, slot, cache.block_table,
                                 cache.page_size, pool, q)
         att = torch.empty(T, L.heads * L.vdim, device=dev, dtype=self.dtype)
-        seqlib.window_attn(q, L.heads, L.kv_heads, L.dim, L.vdim, pool, cache.block_table, cache.page_size, pos, slot, L.window, L.scale,
-                           L.softcap, mw.dist_bias, att)
+        if plans is not None and self.tensor_attention and seqlib.window_attn_mma_ok(L.heads, L.kv_heads, L.dim, L.vdim, self.dtype):
+            rep = L.heads // L.kv_heads
+            if plans["portions"] is None:        # one row per request: the kernel reads positions and slots itself
+                items = None
+            else:
+                items = plans.get(rep)
+                if items is None:
+                    items = plans[rep] = seqlib.window_attn_items(plans["portions"], rep, dev)
+            seqlib.window_attn_mma(q, L.heads, L.kv_heads, L.dim, L.vdim, pool, cache.block_table, cache.page_size, items, pos, slot,
+                                   L.window, L.scale, L.softcap, mw.dist_bias, att)
+        else:
+            seqlib.window_attn(q, L.heads, L.kv_heads, L.dim, L.vdim, pool, cache.block_table, cache.page_size, pos, slot, L.window, L.scale,
+                               L.softcap, mw.dist_bias, att)
         left = self._linear(att, mw.left_o, f32)
         # right: constant-decay outer-product state
         o = torch.empty(T, R.heads * R.vdim, device=dev, dtype=f32)
@@ -361,6 +373,9 @@ class TifisunDecoder:
             row_begin, n_portions = self._arange, T
         else:
             row_begin, n_portions = self._row_begin(T, slot, portions)
+        # work lists of the tensor-core attention kernel, built once per step and head grouping; without the host's view of the
+        # batch (portions) the plain kernel runs
+        plans = {"portions": None} if one_row_each else ({"portions": list(portions)} if portions is not None else None)
         layers, mult = self.w.layers, self.cfg.residual_mult
         h32 = torch.empty(T, self.C, device=dev, dtype=f32)
         xb = torch.empty(T, self.C, device=dev, dtype=self.dtype)
@@ -375,7 +390,7 @@ class TifisunDecoder:
                 y = self._delta(li, xb, pos, slot, cache, row_begin, n_portions)
                 seqlib.post_norm_residual(y, lw.norm1b, self.eps, mult, h32, after_mixer, xb_out)
             else:
-                yl, yr = self._parallel(li, xb, pos, slot, cache, row_begin, n_portions)
+                yl, yr = self._parallel(li, xb, pos, slot, cache, row_begin, n_portions, plans)
                 seqlib.post_norm_residual(yl, lw.norm1b, self.eps, mult, h32, after_mixer, xb_out, y2=yr, wa=lw.mix.left_out,
                                           wb=lw.mix.right_out)
             if lw.mlp is not None:

@@ -31,6 +31,8 @@ SIGNATURES = {
     "omc_gated_rms_rows": (_I, [_P, _L, _I, _I, _I, _P, _I, _F, _P, _L, _I, _P, _I, _L, _P]),
     "omc_qk_norm_kv_store": (_I, [_P, _L, _I, _P, _P, _L, _I, _P, _I, _P, _L, _I, _F, _I, _P, _P, _P, _I, _I, _P, _P, _L, _I, _P]),
     "omc_window_attn": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P, _P, _I, _F, _F, _P, _P, _I, _L, _P]),
+    "omc_window_attn_mma_ok": (_I, [_I, _I, _I, _I]),
+    "omc_window_attn_mma": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _P, _P, _I, _F, _F, _P, _P, _I, _L, _P]),
     "omc_embed_scale": (_I, [_P, _I, _P, _I, _I, _I, _F, _P, _L, _P, _I, _L, _P]),
     "omc_rms_rows": (_I, [_P, _L, _P, _I, _I, _F, _P, _I, _L, _I, _I, _P]),
     "omc_norm_residual": (_I, [_P, _L, _P, _I, _F, _P, _L, _P, _I, _L, _I, _I, _P]),
@@ -436,4 +438,38 @@ def window_attn(q: torch.Tensor, H: int, G: int, d: int, dv: int, pool: torch.Te
                                 block_table.shape[1], page_size, _ptr(pos), _ptr(slot), window, scale, softcap, _ptr(dist_bias), _ptr(out),
                                 _dt(out), out.stride(0), _stream())
     _check(rc, "omc_window_attn")
+    return out
+
+
+def window_attn_mma_ok(H: int, G: int, d: int, dv: int, dtype: torch.dtype) -> bool:
+    """Shapes the tensor-core kernel takes; everything else runs on the plain kernel."""
+    return dtype == torch.bfloat16 and bool(load().omc_window_attn_mma_ok(H, G, d, dv))
+
+
+def window_attn_items(portions, rep: int, device) -> torch.Tensor:
+    """Work list of omc_window_attn_mma for one step: portions [(first_row, n_rows, slot, first_pos)] cut into tiles of 64 // rep
+    tokens (rep = query heads per key/value head) -> int32 [n_items, 4] on the device."""
+    import numpy as np
+    tok = MMA_ROWS // rep
+    parts = []
+    for first_row, n, slot, p0 in portions:
+        st = np.arange(0, n, tok, dtype=np.int32)
+        parts.append(np.stack([first_row + st, np.minimum(tok, n - st), np.full_like(st, slot), p0 + st], axis=1))
+    flat = torch.from_numpy(np.concatenate(parts, axis=0).astype(np.int32))
+    return flat.pin_memory().to(device, non_blocking=True) if torch.device(device).type == "cuda" else flat
+
+
+def window_attn_mma(q: torch.Tensor, H: int, G: int, d: int, dv: int, pool: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                    items: Optional[torch.Tensor], pos, slot, window: int, scale: float, softcap: float,
+                    dist_bias: Optional[torch.Tensor], out: torch.Tensor):
+    """items None: every row of q is a request of its own at (slot[t], pos[t])."""
+    _need_cuda(q, pool, block_table, items, pos, slot, dist_bias, out)
+    assert q.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
+    assert pool.is_contiguous() and pool.shape[-1] == G * (d + dv) and block_table.is_contiguous()
+    assert items is None or (items.dtype == torch.int32 and items.is_contiguous() and items.shape[1] == 4)
+    assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape == (window, H))
+    rc = load().omc_window_attn_mma(_ptr(q), q.stride(0), q.shape[0], H, G, d, dv, _ptr(pool), _ptr(block_table), block_table.shape[1],
+                                    page_size, _ptr(items), items.shape[0] if items is not None else 0, _ptr(pos), _ptr(slot), window,
+                                    scale, softcap, _ptr(dist_bias), _ptr(out), _dt(out), out.stride(0), _stream())
+    _check(rc, "omc_window_attn_mma")
     return out

@@ -70,6 +70,15 @@ def config_c(page=16):
                 parallel(2, 1, 72, 40, 70, 2, 136, 24, [0.5, 0.995], softcap=5.0, bias_max=64, weights_of=0)]}
 
 
+def config_d(page=16):
+    """Attention shapes the tensor-core kernel takes (bf16): grouped heads, a window over several key tiles, two such layers."""
+    return {"architecture": "Tifisun", "vocab": 110, "width": 64, "embedding": {"scale": 3.0}, "residual_mult": 0.7, "norm": {"eps": 1e-5},
+            "kv_page_size": page, "layers": [
+                parallel(4, 2, 32, 16, 75, 2, 16, 32, [0.9, 0.99], softcap=20.0, bias_max=80),
+                delta(2, 2, 32, 32, 4),
+                parallel(8, 1, 16, 64, 9, 1, 32, 16, [0.97], softcap=20.0, bias_max=20, ff=0)]}
+
+
 def build(cfg_dict, dtype, seed=0, edit=None, bias_rows=10):
     cfg = TifisunConfig.from_dict(cfg_dict)
     sd = random_state_dict(cfg, seed=seed, decay_rank=12, gate_rank=20, bias_rows=bias_rows)
@@ -250,8 +259,9 @@ def test_linear_bias_and_gated_halves():
     assert torch.allclose(z.double().cpu(), want, atol=2e-3, rtol=2e-3)
 
 
-def _window_case(H, G, d, dv, window, page, softcap, dtype, q, k, v, rel, far, cuts, wq=None, wk=None):
-    """Runs store + attention over `cuts` portions of one request on shuffled pages; returns [T, H * dv] float64."""
+def _window_case(H, G, d, dv, window, page, softcap, dtype, q, k, v, rel, far, cuts, wq=None, wk=None, mma=False):
+    """Runs store + attention over `cuts` portions of one request on shuffled pages; returns [T, H * dv] float64. mma: the
+    tensor-core kernel (portions of one token go through its list-free decode form)."""
     T = q.shape[0]
     n_pages = -(-T // page) + 2
     pool = torch.full((n_pages, page, G * (d + dv)), float("nan"), device=DEV, dtype=dtype)
@@ -269,7 +279,11 @@ def _window_case(H, G, d, dv, window, page, softcap, dtype, q, k, v, rel, far, c
         qo = torch.empty(hi - lo, H * d, device=DEV, dtype=dtype)
         seqlib.qk_norm_kv_store(_dev(q[lo:hi]), _dev(wq, dtype), _dev(k[lo:hi]), _dev(wk, dtype), _dev(v[lo:hi]), 1e-5, pos, slot, table, page, pool, qo)
         o = torch.empty(hi - lo, H * dv, device=DEV, dtype=dtype)
-        seqlib.window_attn(qo, H, G, d, dv, pool, table, page, pos, slot, window, d ** -0.5, softcap, bias, o)
+        if mma:
+            items = None if hi - lo == 1 else seqlib.window_attn_items([(0, hi - lo, 2, lo)], H // G, DEV)
+            seqlib.window_attn_mma(qo, H, G, d, dv, pool, table, page, items, pos, slot, window, d ** -0.5, softcap, bias, o)
+        else:
+            seqlib.window_attn(qo, H, G, d, dv, pool, table, page, pos, slot, window, d ** -0.5, softcap, bias, o)
         out[lo:hi] = o.double().cpu()
     return out
 
@@ -286,6 +300,47 @@ def test_window_attention_random(H, G, d, dv, window, page):
     assert torch.allclose(got, want, atol=3e-5, rtol=1e-4), (got - want).abs().max()
     got = _window_case(H, G, d, dv, window, page, 7.0, torch.bfloat16, q, k, v, rel, 40.0, [0, 83], wq, wk)
     assert torch.allclose(got, want, atol=6e-2, rtol=6e-2)
+
+
+@pytest.mark.parametrize("H,G,d,dv,window,page", [(4, 2, 32, 16, 37, 16), (2, 2, 64, 64, 70, 8), (8, 1, 16, 128, 100, 32), (16, 4, 128, 128, 130, 64),
+                                                  (1, 1, 48, 32, 64, 16), (64, 1, 16, 16, 5, 16)])
+def test_window_attention_tensor_core(H, G, d, dv, window, page):
+    assert seqlib.window_attn_mma_ok(H, G, d, dv, torch.bfloat16) and not seqlib.window_attn_mma_ok(H, G, d + 4, dv, torch.bfloat16)
+    g = torch.Generator().manual_seed(window + H)
+    T = 150
+    q, k, v = torch.randn(T, H * d, generator=g, dtype=F64), torch.randn(T, G * d, generator=g, dtype=F64), torch.randn(T, G * dv, generator=g, dtype=F64)
+    rel = torch.randn(10, H, generator=g, dtype=F64)
+    # bf16-rounded inputs on both sides: what is left is the rounding of the probabilities and the hardware tanh
+    r16 = lambda t: t.to(torch.bfloat16).double()
+    ones_q, ones_k = torch.ones(H * d, dtype=F64), torch.ones(G * d, dtype=F64)
+    want = O.windowed_attention(r16(O.norm_plain(q, ones_q, 1e-5)), r16(O.norm_plain(k, ones_k, 1e-5)), r16(v), H, G, d ** -0.5, 7.0, rel, 40.0, window)
+    for cuts in ([0, T], [0, 1, 3, 70, 71, 72, 149, 150]):     # whole; portions with single decoded tokens between them
+        got = _window_case(H, G, d, dv, window, page, 7.0, torch.bfloat16, q, k, v, rel, 40.0, cuts, mma=True)
+        assert torch.allclose(got, want, atol=2.5e-2, rtol=2.5e-2), (cuts, (got - want).abs().max())
+
+
+@pytest.mark.parametrize("edge", ["inside", "outside"])
+@pytest.mark.parametrize("decoded", [False, True])
+def test_window_edge_key_on_the_tensor_core_kernel(edge, decoded):
+    H, G, d, dv, window, page, T = 2, 1, 16, 16, 70, 16, 200          # the window spans more than one key tile
+    g = torch.Generator().manual_seed(3)
+    k = torch.randn(T, d, generator=g, dtype=F64) * 0.05
+    v = torch.randn(T, dv, generator=g, dtype=F64)
+    q = torch.randn(T, H * d, generator=g, dtype=F64) * 0.05
+    i = T - 1
+    j = i - window + 1 if edge == "inside" else i - window
+    e = torch.zeros(d, dtype=F64)
+    e[3] = 1.0
+    k[:, 3] = 0.0
+    k[j] = e
+    q[i] = torch.cat([e, e])
+    rel = torch.zeros(10, H, dtype=F64)
+    wq = torch.full((H * d,), 5.0, dtype=F64)
+    got = _window_case(H, G, d, dv, window, page, 1000.0, torch.bfloat16, q, k, v, rel, 40.0, [0, T - 1, T] if decoded else [0, T], wq=wq, mma=True)
+    if edge == "inside":
+        assert torch.allclose(got[i, :dv], v[j], atol=0.05)
+    else:
+        assert (got[i, :dv] - v[j]).abs().max() > 0.3
 
 
 @pytest.mark.parametrize("edge", ["inside", "outside"])
@@ -337,10 +392,10 @@ def test_distance_bias_buckets_show_in_the_scores():
 
 
 # --------------------------------------------------------------------------------------------------------------- whole model
-CONFIGS = {"a": config_a, "b": config_b, "c": config_c}
+CONFIGS = {"a": config_a, "b": config_b, "c": config_c, "d": config_d}
 
 
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_layers_and_logits_against_oracle(name, dtype):
     cd = CONFIGS[name]()
@@ -364,19 +419,19 @@ def test_layers_and_logits_against_oracle(name, dtype):
     assert rel_err(lg, want) < TOL[dtype]
 
 
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_prefill_portions_and_token_by_token_agree_with_oracle(name, dtype):
     cd = CONFIGS[name]()
     model, sd = build(cd, dtype, seed=3)
-    toks = tokens_for(cd, 75, 4)
+    toks = tokens_for(cd, 100 if name == "d" else 75, 4)       # d: past its window of 75
     want = oracle_logits(cd, sd, toks)
     T = len(toks)
     every = list(range(T))
     # whole; token by token (through the captured decode step from the second token on); portions of 2, 1, 17, 2, 30, 3, 20
     whole, _ = run_schedule(model, [([("w", toks, every)], ["w"])], 128)
     single, _ = run_schedule(model, [([("s", [t], [0])], ["s"] if i == T - 1 else []) for i, t in enumerate(toks)], 128)
-    cuts = [0, 2, 3, 20, 22, 52, 55, 75]
+    cuts = [0, 2, 3, 20, 22, 52, 55, 75] + ([100] if T == 100 else [])
     parts, _ = run_schedule(model, [([("p", toks[lo:hi], list(range(hi - lo)))], []) for lo, hi in zip(cuts[:-1], cuts[1:])], 128)
     for got in (whole["w"], single["s"], parts["p"]):
         assert len(got) == T
