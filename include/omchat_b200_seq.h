@@ -141,23 +141,24 @@ int omc_post_norm_residual(const float* y1, long long ld1, const void* wa, const
                            const void* w_post, int w_dt, float eps, float mult, float* h32, long long ldh, const void* w_next,
                            void* xb, int xb_dt, long long ldxb, int rows, int C, void* stream);
 
-/* y[t, c] = act(z[t, c]) * z[t, n + c] for c < n: the two halves of a stacked gate | up projection. z fp32. */
-int omc_glu_mul(const float* z, long long ldz, int rows, int n, int act, void* y, int y_dt, long long ldy, void* stream);
+/* y[t, c] = act(z[t, c]) * z[t, n + c] for c < n: the two halves of a stacked gate | up projection. z of z_dt, fp32 arithmetic. */
+int omc_glu_mul(const void* z, int z_dt, long long ldz, int rows, int n, int act, void* y, int y_dt, long long ldy, void* stream);
 
 /* Causal convolution over time per channel, then silu, then optional unit vectors. Row t is position pos[t] of the request in
  * state slot slot[t]; rows of one request are consecutive and ascending. w [ch, taps] of w_dt: the last tap multiplies the row
  * itself, tap j the input taps - 1 - j positions back - an earlier row of the step, else state[slot][position % (taps - 1)][ch]
  * (fp32 ring of the last taps - 1 inputs, updated by this call), else zero before position 0. Of the outputs the first
  * unit_channels are divided, in groups of unit_group, by sqrt(sum of squares + unit_eps); the first scaled_channels of those are
- * then multiplied by unit_mult. x / y fp32 (y may not alias x). */
+ * then multiplied by unit_mult (scaled_channels a multiple of unit_group). x / y fp32 (y may not alias x). single_rows != 0: the
+ * caller vouches that every row is a request of its own (a decode step); the ring is then updated by the same launch. */
 int omc_causal_conv_silu(const float* x, long long ldx, int T, int ch, const void* w, int w_dt, int taps, const int32_t* pos,
                          const int32_t* slot, float* state, float* y, long long ldy, int unit_channels, int unit_group,
-                         float unit_eps, int scaled_channels, float unit_mult, void* stream);
+                         float unit_eps, int scaled_channels, float unit_mult, int single_rows, void* stream);
 
 /* Linear-state recurrence per head with an fp32 state S [dim, vdim] in state[slot][head]:
  *   S <- diag(g_t) S;  u_t = beta_t (v_t - S^T k_t) (beta != NULL) or v_t;  S <- S + k_t u_t^T;  o_t = S^T q_t.
  * decay_mode 0: g = decay_const[head]; 1: g = exp(-exp(A_log[head]) softplus(a[t, head] + dt_bias[head])); 2: one decay per key
- * channel, a [T, H * dim], dt_bias [H * dim]. beta raw [T, H], squashed by a sigmoid here. silu_in: q, k, v pass silu first.
+ * channel, a [T, H * dim], dt_bias [H * dim]; 3: a [T, H * dim] holds the decays themselves. beta raw [T, H], squashed by a sigmoid here. silu_in: q, k, v pass silu first.
  * q / k [T, G * dim] (head h reads group h / (H / G)), v [T, H * vdim], out fp32 [T, H * vdim]. Portion i is rows
  * row_begin[i] .. row_begin[i + 1] - 1 (device int32 [portions + 1]), all of slot[row_begin[i]]; a portion whose first row has
  * position 0 starts from S = 0. Tokens are processed one after the other in every case. dim <= 256. */
@@ -195,6 +196,10 @@ int omc_window_attn_mma_ok(int H, int G, int d, int dv);
 int omc_window_attn_mma(const void* q, long long ldq, int T, int H, int G, int d, int dv, const void* pool, const int32_t* block_table,
                         int max_pages, int page_size, const int32_t* items, int n_items, const int32_t* pos, const int32_t* slot,
                         int window, float scale, float softcap, const float* dist_bias, void* out, int out_dt, long long ldo, void* stream);
+
+/* In place over x[t, :cols] (fp32): op 1: silu; op 2: x <- exp(-exp(A_log[c / group]) * softplus(x + bias[c])) - the same
+ * functions the recurrence applies while staging, as one pass for steps with long portions. */
+int omc_map_rows(float* x, long long ldx, int rows, int cols, int op, const float* A_log, const float* bias, int group, void* stream);
 
 #ifdef __cplusplus
 }

@@ -115,16 +115,16 @@ __global__ void __launch_bounds__(256) post_norm_residual_kernel(const float* __
   for (int c = threadIdx.x; c < C; c += blockDim.x) stf(xb + t * ldxb + c, row[c] * rn * (1.f + ldf(w_next + c)));
 }
 
-// out = act(gate) * up over the two halves of a stacked projection: z [rows, 2 * n] fp32 -> out [rows, n].
-template <typename TY>
-__global__ void __launch_bounds__(256) glu_mul_kernel(const float* __restrict__ z, long long ldz, int n, int act, TY* __restrict__ y,
+// out = act(gate) * up over the two halves of a stacked projection: z [rows, 2 * n] -> out [rows, n]; the arithmetic is fp32.
+template <typename TZ, typename TY>
+__global__ void __launch_bounds__(256) glu_mul_kernel(const TZ* __restrict__ z, long long ldz, int n, int act, TY* __restrict__ y,
                                                       long long ldy, long long total) {
   const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= total) return;
   const long long t = e / n;
   const int c = (int)(e - t * n);
-  float g = z[t * ldz + c];
-  const float u = z[t * ldz + n + c];
+  float g = ldf(z + t * ldz + c);
+  const float u = ldf(z + t * ldz + n + c);
   if (act == OMC_ACT_GELU_TANH) g = 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
   else if (act == OMC_ACT_RELU2) g = fmaxf(g, 0.f) * fmaxf(g, 0.f);
   stf(y + t * ldy + c, g * u);
@@ -186,13 +186,13 @@ extern "C" int omc_post_norm_residual(const float* y1, long long ld1, const void
   return check_launch("omc_post_norm_residual");
 }
 
-extern "C" int omc_glu_mul(const float* z, long long ldz, int rows, int n, int act, void* y, int y_dt, long long ldy, void* stream) {
+extern "C" int omc_glu_mul(const void* z, int z_dt, long long ldz, int rows, int n, int act, void* y, int y_dt, long long ldy, void* stream) {
   if (z == nullptr || y == nullptr || rows < 0 || n <= 0) return set_error(OMC_ERR_ARG, "omc_glu_mul: bad argument");
   if (rows == 0) return OMC_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long total = (long long)rows * n;
-  OMC_DT_SWITCH(y_dt, TY, {
-    glu_mul_kernel<TY><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(z, ldz, n, act, static_cast<TY*>(y), ldy, total);
-  })
+  OMC_DT_SWITCH(z_dt, TZ, OMC_DT_SWITCH(y_dt, TY, {
+    glu_mul_kernel<TZ, TY><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(static_cast<const TZ*>(z), ldz, n, act, static_cast<TY*>(y), ldy, total);
+  }))
   return check_launch("omc_glu_mul");
 }

@@ -10,8 +10,8 @@
 // The recurrence is evaluated token by token in every case - prompt portions and single decoded tokens run the same
 // instructions in the same order, which makes the result independent of how a prompt is cut. Its parallelism is over the
 // independent COLUMNS of S: column j of a head's state only ever meets v[:, j], so a CTA owns 32 columns of one head of one
-// portion, four lanes share a column (each holds a quarter of its state elements in registers) and finish the two dot products of
-// a token with two shuffles each. Tokens are staged 16 at a time in shared memory by cp.async, one chunk ahead of the one being
+// portion, eight lanes share a column (each holds an eighth of its state elements in registers, as packed fp32 pairs) and finish the
+// two dot products of a token with three shuffles each. Tokens are staged 16 at a time in shared memory by cp.async, one chunk ahead of the one being
 // computed (decays, sigmoid and silu applied in place on arrival), so the sequential loop touches registers and shared memory only.
 #include "seq_common.cuh"
 
@@ -22,18 +22,22 @@ __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-
 __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 
 // ---- causal convolution + silu (+ unit vectors) ---------------------------------------------------------------------------
-// One CTA per row. Tap j of `taps` multiplies the input `taps - 1 - j` positions back: an earlier row of the same step when that
-// row belongs to the same request, else the state ring state[slot][position % (taps - 1)][channel], else (before position 0) zero.
+// One CTA per (row, block of channels; blocks are whole unit-vector groups). Tap j of `taps` multiplies the input
+// `taps - 1 - j` positions back: an earlier row of the same step when that row belongs to the same request, else the state ring
+// state[slot][position % (taps - 1)][channel], else (before position 0) zero. save_here: every row of the step is a request of
+// its own, so the row's input goes into its ring from this kernel, after the reads (no other CTA reads that ring).
 template <typename TW>
-__global__ void __launch_bounds__(256) causal_conv_silu_kernel(const float* __restrict__ x, long long ldx, int ch,
+__global__ void __launch_bounds__(256) causal_conv_silu_kernel(const float* __restrict__ x, long long ldx, int ch, int ch_block,
                                                                const TW* __restrict__ w, int taps, const int32_t* __restrict__ pos,
-                                                               const int32_t* __restrict__ slot, const float* __restrict__ state,
+                                                               const int32_t* __restrict__ slot, float* __restrict__ state,
                                                                float* __restrict__ y, long long ldy, int unit_channels,
-                                                               int unit_group, float unit_eps, int scaled_channels, float unit_mult) {
-  extern __shared__ float row[];  // [ch]
-  const int t = blockIdx.x;
+                                                               int unit_group, float unit_eps, int scaled_channels, float unit_mult,
+                                                               int save_here) {
+  extern __shared__ float row[];  // [ch_block]
+  const int t = blockIdx.x, c0 = blockIdx.y * ch_block, nc = min(ch_block, ch - c0);
   const int p = pos[t], s = slot[t], R = taps - 1;
-  for (int c = threadIdx.x; c < ch; c += blockDim.x) {
+  for (int cl = threadIdx.x; cl < nc; cl += blockDim.x) {
+    const int c = c0 + cl;
     float acc = 0.f;
     for (int j = 0; j < taps; ++j) {
       const int back = R - j, sp = p - back;
@@ -43,11 +47,16 @@ __global__ void __launch_bounds__(256) causal_conv_silu_kernel(const float* __re
       else xv = state[((long long)s * R + sp % R) * ch + c];
       acc = fmaf(ldf(w + (long long)c * taps + j), xv, acc);
     }
-    row[c] = silu_f(acc);
+    row[cl] = silu_f(acc);
   }
   __syncthreads();
+  if (save_here && R > 0) {
+    float* dst = state + ((long long)s * R + p % R) * ch;
+    for (int cl = threadIdx.x; cl < nc; cl += blockDim.x) dst[c0 + cl] = x[(long long)t * ldx + c0 + cl];
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  const int groups = unit_group > 0 ? unit_channels / unit_group : 0;
+  const int unit_here = max(0, min(nc, unit_channels - c0));      // unit-vector channels of this block (whole groups)
+  const int groups = unit_group > 0 ? unit_here / unit_group : 0;
   for (int g = warp; g < groups; g += nw) {
     float ss = 0.f;
     for (int c = lane; c < unit_group; c += 32) {
@@ -55,15 +64,16 @@ __global__ void __launch_bounds__(256) causal_conv_silu_kernel(const float* __re
       ss = fmaf(v, v, ss);
     }
     ss = seq_warp_sum(ss);
-    const float f = (1.f / sqrtf(ss + unit_eps)) * (g * unit_group < scaled_channels ? unit_mult : 1.f);
+    const float f = (1.f / sqrtf(ss + unit_eps)) * (c0 + g * unit_group < scaled_channels ? unit_mult : 1.f);
     for (int c = lane; c < unit_group; c += 32) row[g * unit_group + c] *= f;
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < ch; c += blockDim.x) y[(long long)t * ldy + c] = row[c];
+  for (int cl = threadIdx.x; cl < nc; cl += blockDim.x) y[(long long)t * ldy + c0 + cl] = row[cl];
 }
 
 // The last taps - 1 inputs of every request of the step go into its ring (rows that are followed by taps - 1 more rows of the
-// same request are not among them).
+// same request are not among them). A launch of its own when a request may have several rows: a row's ring entry is read by
+// CTAs of other rows of the convolution kernel.
 __global__ void __launch_bounds__(256) conv_state_save_kernel(const float* __restrict__ x, long long ldx, int ch, int R, int T,
                                                               const int32_t* __restrict__ pos, const int32_t* __restrict__ slot,
                                                               float* __restrict__ state) {
@@ -71,11 +81,11 @@ __global__ void __launch_bounds__(256) conv_state_save_kernel(const float* __res
   const int s = slot[t];
   if (t + R < T && slot[t + R] == s) return;
   float* dst = state + ((long long)s * R + pos[t] % R) * ch;
-  for (int c = threadIdx.x; c < ch; c += blockDim.x) dst[c] = x[(long long)t * ldx + c];
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < ch; c += gridDim.y * blockDim.x) dst[c] = x[(long long)t * ldx + c];
 }
 
 // ---- linear-state recurrence ----------------------------------------------------------------------------------------------
-constexpr int kScanCols = 32, kScanLanes = 4, kScanTok = 16;
+constexpr int kScanCols = 32, kScanLanes = 8, kScanTok = 16;
 
 struct ScanArgs {
   const float* q;      // [T, ldq]: head g of kv_heads at columns g * dim
@@ -83,7 +93,7 @@ struct ScanArgs {
   const float* v;      // [T, ldv]: head h at columns h * vdim
   long long ldq, ldk, ldv;
   int silu_in;         // q, k, v pass silu on the way in
-  int decay_mode;      // 0: decay_const[h]; 1: a[t, h]; 2: a[t, h * dim + i]  (1, 2: g = exp(-exp(A_log[h]) softplus(a + dt_bias)))
+  int decay_mode;      // 0: decay_const[h]; 1: a[t, h]; 2: a[t, h * dim + i]  (1, 2: g = exp(-exp(A_log[h]) softplus(a + dt_bias))); 3: g = a[t, h * dim + i]
   const float* decay_const;
   const float* a;
   long long lda;
@@ -107,8 +117,33 @@ __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src));
 }
 
+// Packed fp32 pairs (sm_100: one instruction, two IEEE fp32 operations): the recurrence's state lives in such pairs.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float sum2(f32x2 a, f32x2 b) {
+  float a0, a1, b0, b1;
+  unpack2(a, a0, a1);
+  unpack2(b, b0, b1);
+  return (a0 + a1) + (b0 + b1);
+}
+
 // Shared-memory place of key channel i: lane l = i / DPT owns DPT consecutive channels (read as float4), and a gap of four floats
-// between the lanes' blocks moves them to different banks.
+// between the lanes' blocks moves them to different banks (strides of 12, 20 and 36 floats spread eight float4 reads over all 32).
 template <int DPT>
 __device__ __forceinline__ int scan_place(int i) { return (i / DPT) * (DPT + 4) + (i % DPT); }
 
@@ -120,24 +155,25 @@ __global__ void __launch_bounds__(kScanCols * kScanLanes) linear_state_scan_kern
   extern __shared__ __align__(16) float sm[];
   constexpr int PITCH = kScanLanes * (DPT + 4);
   const int dim = a.dim;
-  const bool chan = a.decay_mode == 2;
+  const bool chan = a.decay_mode >= 2;   // one decay per key channel: computed here (2) or given (3)
   const int stage_floats = kScanTok * PITCH * (chan ? 3 : 2) + kScanTok * kScanCols + 2 * kScanTok;
   const int h = blockIdx.y, kvh = h / (a.H / a.G);
   const int col0 = blockIdx.x * kScanCols;
   const int r0 = a.row_begin[blockIdx.z], r1 = a.row_begin[blockIdx.z + 1];
   if (r1 <= r0) return;
-  const int tid = threadIdx.x, lane = tid & (kScanLanes - 1), col = col0 + (tid >> 2);
+  const int tid = threadIdx.x, lane = tid & (kScanLanes - 1), col = col0 + (tid / kScanLanes);
   const bool col_ok = col < a.vdim;
   for (int e = tid; e < 2 * stage_floats; e += blockDim.x) sm[e] = 0.f;   // the pads stay zero: they meet zero state only
   float* S = a.state + (((long long)a.slot[r0] * a.H + h) * dim) * a.vdim;
-  float st[DPT];
+  f32x2 st[DPT / 2];   // this thread's DPT state elements of its column, as pairs of neighbouring key channels
   const bool fresh = a.pos[r0] == 0;
 #pragma unroll
-  for (int r = 0; r < DPT; ++r) {
+  for (int r = 0; r < DPT; r += 2) {
     const int i = lane * DPT + r;
-    st[r] = (!fresh && col_ok && i < dim) ? S[(long long)i * a.vdim + col] : 0.f;
+    const bool ld = !fresh && col_ok;
+    st[r / 2] = pack2((ld && i < dim) ? S[(long long)i * a.vdim + col] : 0.f, (ld && i + 1 < dim) ? S[(long long)(i + 1) * a.vdim + col] : 0.f);
   }
-  const float A = a.decay_mode != 0 ? expf(a.A_log[h]) : 0.f;
+  const float A = (a.decay_mode == 1 || a.decay_mode == 2) ? expf(a.A_log[h]) : 0.f;
   const float gconst = a.decay_mode == 0 ? a.decay_const[h] : 1.f;
   __syncthreads();
 
@@ -195,14 +231,14 @@ __global__ void __launch_bounds__(kScanCols * kScanLanes) linear_state_scan_kern
     float* sv = sg + (chan ? kScanTok * PITCH : kScanTok);
     float* sb = sv + kScanTok * kScanCols;
     // raw inputs -> what the recurrence uses
-    if (a.silu_in || chan) {
+    if (a.silu_in || a.decay_mode == 2) {
       for (int e = tid; e < n * dim; e += blockDim.x) {
         const int tt = e / dim, i = e - tt * dim, at = tt * PITCH + scan_place<DPT>(i);
         if (a.silu_in) {
           sk[at] = silu_f(sk[at]);
           sq[at] = silu_f(sq[at]);
         }
-        if (chan) sg[at] = expf(-A * softplus_f(sg[at] + a.dt_bias[h * dim + i]));
+        if (a.decay_mode == 2) sg[at] = expf(-A * softplus_f(sg[at] + a.dt_bias[h * dim + i]));
       }
     }
     if (a.silu_in)
@@ -216,54 +252,81 @@ __global__ void __launch_bounds__(kScanCols * kScanLanes) linear_state_scan_kern
     for (int tt = 0; tt < n; ++tt) {
       const float* kr = sk + tt * PITCH + lane * (DPT + 4);
       const float* qr = sq + tt * PITCH + lane * (DPT + 4);
-      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+      f32x2 da = 0ull, db = 0ull;   // two packed accumulators = four partial sums
       if (chan) {
         const float* gr = sg + tt * PITCH + lane * (DPT + 4);
 #pragma unroll
         for (int r = 0; r < DPT; r += 4) {
-          const float4 kv = *reinterpret_cast<const float4*>(kr + r);
-          const float4 gv = *reinterpret_cast<const float4*>(gr + r);
-          st[r] *= gv.x, st[r + 1] *= gv.y, st[r + 2] *= gv.z, st[r + 3] *= gv.w;
-          d0 = fmaf(st[r], kv.x, d0), d1 = fmaf(st[r + 1], kv.y, d1), d2 = fmaf(st[r + 2], kv.z, d2), d3 = fmaf(st[r + 3], kv.w, d3);
+          const ulonglong2 kv = *reinterpret_cast<const ulonglong2*>(kr + r);
+          const ulonglong2 gv = *reinterpret_cast<const ulonglong2*>(gr + r);
+          st[r / 2] = mul2(st[r / 2], gv.x);
+          st[r / 2 + 1] = mul2(st[r / 2 + 1], gv.y);
+          da = fma2(st[r / 2], kv.x, da);
+          db = fma2(st[r / 2 + 1], kv.y, db);
         }
       } else {
-        const float g = sg[tt];
+        const f32x2 g2 = pack2(sg[tt], sg[tt]);
 #pragma unroll
         for (int r = 0; r < DPT; r += 4) {
-          const float4 kv = *reinterpret_cast<const float4*>(kr + r);
-          st[r] *= g, st[r + 1] *= g, st[r + 2] *= g, st[r + 3] *= g;
-          d0 = fmaf(st[r], kv.x, d0), d1 = fmaf(st[r + 1], kv.y, d1), d2 = fmaf(st[r + 2], kv.z, d2), d3 = fmaf(st[r + 3], kv.w, d3);
+          const ulonglong2 kv = *reinterpret_cast<const ulonglong2*>(kr + r);
+          st[r / 2] = mul2(st[r / 2], g2);
+          st[r / 2 + 1] = mul2(st[r / 2 + 1], g2);
+          da = fma2(st[r / 2], kv.x, da);
+          db = fma2(st[r / 2 + 1], kv.y, db);
         }
       }
-      float u = sv[tt * kScanCols + (tid >> 2)];
+      float u = sv[tt * kScanCols + (tid / kScanLanes)];
       if (a.beta != nullptr) {
-        float dot = (d0 + d1) + (d2 + d3);
+        float dot = sum2(da, db);
         dot += __shfl_xor_sync(0xffffffffu, dot, 1);
         dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
         u = sb[tt] * (u - dot);
       }
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      const f32x2 u2 = pack2(u, u);
+      f32x2 oa = 0ull, ob = 0ull;
 #pragma unroll
       for (int r = 0; r < DPT; r += 4) {
-        const float4 kv = *reinterpret_cast<const float4*>(kr + r);
-        const float4 qv = *reinterpret_cast<const float4*>(qr + r);
-        st[r] = fmaf(kv.x, u, st[r]), st[r + 1] = fmaf(kv.y, u, st[r + 1]), st[r + 2] = fmaf(kv.z, u, st[r + 2]), st[r + 3] = fmaf(kv.w, u, st[r + 3]);
-        o0 = fmaf(st[r], qv.x, o0), o1 = fmaf(st[r + 1], qv.y, o1), o2 = fmaf(st[r + 2], qv.z, o2), o3 = fmaf(st[r + 3], qv.w, o3);
+        const ulonglong2 kv = *reinterpret_cast<const ulonglong2*>(kr + r);
+        const ulonglong2 qv = *reinterpret_cast<const ulonglong2*>(qr + r);
+        st[r / 2] = fma2(kv.x, u2, st[r / 2]);
+        st[r / 2 + 1] = fma2(kv.y, u2, st[r / 2 + 1]);
+        oa = fma2(st[r / 2], qv.x, oa);
+        ob = fma2(st[r / 2 + 1], qv.y, ob);
       }
-      float o = (o0 + o1) + (o2 + o3);
+      float o = sum2(oa, ob);
       o += __shfl_xor_sync(0xffffffffu, o, 1);
       o += __shfl_xor_sync(0xffffffffu, o, 2);
+      o += __shfl_xor_sync(0xffffffffu, o, 4);
       if (lane == 0 && col_ok) a.out[(long long)(c0 + tt) * a.ldo + h * a.vdim + col] = o;
     }
     __syncthreads();   // the next iteration's copies overwrite the stage that was just read
   }
   if (col_ok) {
 #pragma unroll
-    for (int r = 0; r < DPT; ++r) {
+    for (int r = 0; r < DPT; r += 2) {
       const int i = lane * DPT + r;
-      if (i < dim) S[(long long)i * a.vdim + col] = st[r];
+      float lo, hi;
+      unpack2(st[r / 2], lo, hi);
+      if (i < dim) S[(long long)i * a.vdim + col] = lo;
+      if (i + 1 < dim) S[(long long)(i + 1) * a.vdim + col] = hi;
     }
   }
+}
+
+// ---- elementwise preparation of a recurrence's inputs --------------------------------------------------------------------
+// In place over x[t, :cols]: op 1: silu; op 2: x <- exp(-exp(A_log[c / group]) * softplus(x + bias[c])), the per-channel decay.
+// The recurrence can do both itself while it stages its inputs; for long portions one pass here is cheaper than doing it in
+// every CTA that shares a head.
+__global__ void __launch_bounds__(256) map_rows_kernel(float* __restrict__ x, long long ldx, int cols, long long total, int op,
+                                                       const float* __restrict__ A_log, const float* __restrict__ bias, int group) {
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= total) return;
+  const long long t = e / cols;
+  const int c = (int)(e - t * cols);
+  float* p = x + t * ldx + c;
+  if (op == 1) *p = silu_f(*p);
+  else *p = expf(-expf(A_log[c / group]) * softplus_f(*p + bias[c]));
 }
 
 // ---- gated RMS norm over groups of a row ----------------------------------------------------------------------------------
@@ -298,20 +361,28 @@ using namespace omc;
 extern "C" int omc_causal_conv_silu(const float* x, long long ldx, int T, int ch, const void* w, int w_dt, int taps,
                                     const int32_t* pos, const int32_t* slot, float* state, float* y, long long ldy,
                                     int unit_channels, int unit_group, float unit_eps, int scaled_channels, float unit_mult,
-                                    void* stream) {
+                                    int single_rows, void* stream) {
   if (x == nullptr || w == nullptr || pos == nullptr || slot == nullptr || y == nullptr || T < 0 || ch <= 0 || taps < 1 ||
-      (taps > 1 && state == nullptr) || unit_channels < 0 || unit_channels > ch || (unit_channels > 0 && (unit_group <= 0 || unit_channels % unit_group)))
+      (taps > 1 && state == nullptr) || unit_channels < 0 || unit_channels > ch || (unit_channels > 0 && (unit_group <= 0 || unit_channels % unit_group)) ||
+      (unit_channels > 0 && scaled_channels % unit_group))
     return set_error(OMC_ERR_ARG, "omc_causal_conv_silu: bad argument");
   if (T == 0) return OMC_OK;
-  if ((size_t)ch * sizeof(float) > 200 * 1024) return set_error(OMC_ERR_SHAPE, "omc_causal_conv_silu: too many channels for one row in shared memory");
+  // channel blocks of about 512 channels, whole unit-vector groups each
+  int ch_block = 512;
+  if (unit_channels > 0) ch_block = unit_group >= 512 ? unit_group : (512 / unit_group) * unit_group;
+  if (ch_block > ch) ch_block = ch;
+  if ((size_t)ch_block * sizeof(float) > 200 * 1024) return set_error(OMC_ERR_SHAPE, "omc_causal_conv_silu: unit-vector group too wide for shared memory");
+  const int blocks = (ch + ch_block - 1) / ch_block;
+  if (blocks > 65535) return set_error(OMC_ERR_SHAPE, "omc_causal_conv_silu: too many channel blocks");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const size_t smem = (size_t)ch * sizeof(float);
+  const size_t smem = (size_t)ch_block * sizeof(float);
   OMC_DT_SWITCH(w_dt, TW, {
     if (smem > 48 * 1024) cudaFuncSetAttribute(causal_conv_silu_kernel<TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    causal_conv_silu_kernel<TW><<<T, 256, smem, st>>>(x, ldx, ch, static_cast<const TW*>(w), taps, pos, slot, state, y, ldy,
-                                                      unit_channels, unit_group, unit_eps, scaled_channels, unit_mult);
+    causal_conv_silu_kernel<TW><<<dim3(T, blocks), 256, smem, st>>>(x, ldx, ch, ch_block, static_cast<const TW*>(w), taps, pos, slot, state, y,
+                                                                    ldy, unit_channels, unit_group, unit_eps, scaled_channels, unit_mult,
+                                                                    single_rows ? 1 : 0);
   })
-  if (taps > 1) conv_state_save_kernel<<<T, 256, 0, st>>>(x, ldx, ch, taps - 1, T, pos, slot, state);
+  if (taps > 1 && !single_rows) conv_state_save_kernel<<<dim3(T, (ch + 1023) / 1024), 256, 0, st>>>(x, ldx, ch, taps - 1, T, pos, slot, state);
   return check_launch("omc_causal_conv_silu");
 }
 
@@ -321,8 +392,9 @@ extern "C" int omc_linear_state_scan(const float* q, long long ldq, const float*
                                      float* out, long long ldo, const int32_t* row_begin, int portions, const int32_t* pos,
                                      const int32_t* slot, int H, int G, int dim, int vdim, void* stream) {
   if (q == nullptr || k == nullptr || v == nullptr || state == nullptr || out == nullptr || row_begin == nullptr || pos == nullptr ||
-      slot == nullptr || portions < 0 || H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || decay_mode < 0 || decay_mode > 2 ||
-      (decay_mode == 0 && decay_const == nullptr) || (decay_mode != 0 && (a == nullptr || A_log == nullptr || dt_bias == nullptr)))
+      slot == nullptr || portions < 0 || H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || decay_mode < 0 || decay_mode > 3 ||
+      (decay_mode == 0 && decay_const == nullptr) || (decay_mode != 0 && a == nullptr) ||
+      ((decay_mode == 1 || decay_mode == 2) && (A_log == nullptr || dt_bias == nullptr)))
     return set_error(OMC_ERR_ARG, "omc_linear_state_scan: bad argument");
   if (portions == 0) return OMC_OK;
   if (dim > 256) return set_error(OMC_ERR_SHAPE, "omc_linear_state_scan: key width above 256");
@@ -330,14 +402,14 @@ extern "C" int omc_linear_state_scan(const float* q, long long ldq, const float*
   ScanArgs s{q, k, v, ldq, ldk, ldv, silu_in, decay_mode, decay_const, a, lda, A_log, dt_bias, beta, ldb, state, out, ldo,
              row_begin, pos, slot, H, G, dim, vdim};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int dpt = dim <= 32 ? 8 : (dim <= 64 ? 16 : (dim <= 128 ? 32 : 64));
-  const size_t stage_floats = (size_t)kScanTok * kScanLanes * (dpt + 4) * (decay_mode == 2 ? 3 : 2) + kScanTok * kScanCols + 2 * kScanTok;
+  const int dpt = dim <= 32 ? 4 : (dim <= 64 ? 8 : (dim <= 128 ? 16 : 32));   // state elements per thread: dim / 8 lanes, rounded up
+  const size_t stage_floats = (size_t)kScanTok * kScanLanes * (dpt + 4) * (decay_mode >= 2 ? 3 : 2) + kScanTok * kScanCols + 2 * kScanTok;
   const size_t smem = 2 * stage_floats * sizeof(float);
   dim3 grid((vdim + kScanCols - 1) / kScanCols, H, portions);
   const int threads = kScanCols * kScanLanes;
   auto al16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   const bool vec = dim % 4 == 0 && vdim % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ldv % 4 == 0 && al16(q) && al16(k) && al16(v) &&
-                   (decay_mode != 2 || (lda % 4 == 0 && al16(a)));
+                   (decay_mode < 2 || (lda % 4 == 0 && al16(a)));
 #define OMC_SCAN_LAUNCH(DPT, VEC)                                                                                        \
   do {                                                                                                                   \
     static bool attr_done[kMaxDevices] = {};                                                                             \
@@ -352,10 +424,10 @@ extern "C" int omc_linear_state_scan(const float* q, long long ldq, const float*
     if (vec) OMC_SCAN_LAUNCH(DPT, true); \
     else OMC_SCAN_LAUNCH(DPT, false);    \
   } while (0)
-  if (dpt == 8) OMC_SCAN_DPT(8);
+  if (dpt == 4) OMC_SCAN_DPT(4);
+  else if (dpt == 8) OMC_SCAN_DPT(8);
   else if (dpt == 16) OMC_SCAN_DPT(16);
-  else if (dpt == 32) OMC_SCAN_DPT(32);
-  else OMC_SCAN_DPT(64);
+  else OMC_SCAN_DPT(32);
 #undef OMC_SCAN_DPT
 #undef OMC_SCAN_LAUNCH
   return check_launch("omc_linear_state_scan");
@@ -373,4 +445,14 @@ extern "C" int omc_gated_rms_rows(const float* x, long long ldx, int rows, int g
                                                                                  gate, ldg, gate_act, static_cast<TY*>(y), ldy);
   }))
   return check_launch("omc_gated_rms_rows");
+}
+
+extern "C" int omc_map_rows(float* x, long long ldx, int rows, int cols, int op, const float* A_log, const float* bias, int group,
+                            void* stream) {
+  if (x == nullptr || rows < 0 || cols <= 0 || (op != 1 && op != 2) || (op == 2 && (A_log == nullptr || bias == nullptr || group <= 0)))
+    return set_error(OMC_ERR_ARG, "omc_map_rows: bad argument");
+  if (rows == 0) return OMC_OK;
+  const long long total = (long long)rows * cols;
+  map_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, ldx, cols, total, op, A_log, bias, group);
+  return check_launch("omc_map_rows");
 }

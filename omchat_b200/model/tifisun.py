@@ -242,6 +242,9 @@ def random_state_dict(cfg: TifisunConfig, seed: int = 0, decay_rank: int = 16, g
 
 
 # ------------------------------------------------------------------------------------------------------------------- decoder
+PREP_MIN_ROWS = 32   # average rows per request from which silu / decays of a recurrence's inputs are a pass of their own
+
+
 class TifisunDecoder:
     def __init__(self, cfg: TifisunConfig, w: TifisunW, dtype: torch.dtype):
         self.cfg, self.w, self.dtype = cfg, w, dtype
@@ -291,14 +294,19 @@ class TifisunDecoder:
         nqk = G * d
         qkv = torch.empty(T, 2 * nqk + H * dv, device=dev, dtype=f32)
         seqlib.causal_conv_silu(z[:, :2 * nqk + H * dv], mw.conv, pos, slot, st.get("conv"), qkv, unit_channels=2 * nqk, unit_group=d,
-                                unit_eps=1e-6, scaled_channels=nqk, unit_mult=d ** -0.5)
+                                unit_eps=1e-6, scaled_channels=nqk, unit_mult=d ** -0.5, single_rows=n_portions == T)
         a, gate = z[:, mw.cols["a"]], z[:, mw.cols["g"]]
         if m.channel_decay:
             a = self._linear(a, mw.a2, f32)                              # [T, H * d]
             gate = self._linear(gate, mw.g2, f32)                        # [T, H * dv]
         o = torch.empty(T, H * dv, device=dev, dtype=f32)
+        # long portions: the per-channel decays in one pass instead of in every CTA that shares a head (the same function either way)
+        prep = m.channel_decay and T >= PREP_MIN_ROWS * n_portions
+        if prep:
+            seqlib.map_rows(a, seqlib.MAP_DECAY, mw.A_log, mw.dt_bias, d)
         seqlib.linear_state_scan(qkv[:, :nqk], qkv[:, nqk:2 * nqk], qkv[:, 2 * nqk:], st["S"], o, row_begin, n_portions, pos, slot, H, G, d, dv,
-                                 a=a, A_log=mw.A_log, dt_bias=mw.dt_bias, channel_decay=m.channel_decay, beta=z[:, mw.cols["beta"]])
+                                 a=a, A_log=mw.A_log, dt_bias=mw.dt_bias, channel_decay=m.channel_decay, beta=z[:, mw.cols["beta"]],
+                                 decay_given=prep)
         on = torch.empty(T, H * dv, device=dev, dtype=self.dtype)
         seqlib.gated_rms_rows(o, H, dv, mw.norm, self.eps, gate, seqlib.GATE_SIGMOID if m.channel_decay else seqlib.GATE_SILU, on)
         return self._linear(on, mw.o, f32)
@@ -332,8 +340,11 @@ class TifisunDecoder:
         left = self._linear(att, mw.left_o, f32)
         # right: constant-decay outer-product state
         o = torch.empty(T, R.heads * R.vdim, device=dev, dtype=f32)
+        prep = T >= PREP_MIN_ROWS * n_portions
+        if prep:   # q | k | v are neighbours in the stacked projection: one pass of silu over the three
+            seqlib.map_rows(z[:, c["rq"].start:c["rv"].stop], seqlib.MAP_SILU)
         seqlib.linear_state_scan(z[:, c["rq"]], z[:, c["rk"]], z[:, c["rv"]], cache.states[li]["S"], o, row_begin, n_portions, pos, slot,
-                                 R.heads, R.heads, R.dim, R.vdim, silu_in=True, decay_const=mw.decay)
+                                 R.heads, R.heads, R.dim, R.vdim, silu_in=not prep, decay_const=mw.decay)
         on = torch.empty(T, R.heads * R.vdim, device=dev, dtype=self.dtype)
         seqlib.gated_rms_rows(o, 1, R.heads * R.vdim, mw.right_norm, self.eps, z[:, c["rg"]], seqlib.GATE_SIGMOID, on)
         right = self._linear(on, mw.right_o, f32)
@@ -395,7 +406,7 @@ class TifisunDecoder:
                                           wb=lw.mix.right_out)
             if lw.mlp is not None:
                 ff = lw.mlp.down.shape[1]
-                z = self._linear(xb, lw.mlp.gate_up, f32, bias=lw.mlp.gate_up_b)
+                z = self._linear(xb, lw.mlp.gate_up, self.dtype, bias=lw.mlp.gate_up_b)   # gate | up in the compute dtype
                 act = seqlib.glu_mul(z, ff, seqlib.ACT_GELU_TANH, torch.empty(T, ff, device=dev, dtype=self.dtype))
                 y = self._linear(act, lw.mlp.down, f32, bias=lw.mlp.down_b)
                 seqlib.post_norm_residual(y, lw.norm2b, self.eps, mult, h32, nxt, None if last else xb)

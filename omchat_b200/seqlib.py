@@ -25,9 +25,10 @@ SIGNATURES = {
     "omc_linear": (_I, [_P, _I, _L, _L, _P, _I, _L, _L, _P, _I, _L, _L, _I, _I, _I, _I, _F, _I, _P, _L, _P]),
     "omc_linear_bias": (_I, [_P, _I, _L, _L, _P, _I, _L, _L, _P, _I, _L, _L, _I, _I, _I, _I, _F, _I, _P, _L, _P, _L, _P]),
     "omc_post_norm_residual": (_I, [_P, _L, _P, _P, _L, _P, _P, _I, _F, _F, _P, _L, _P, _P, _I, _L, _I, _I, _P]),
-    "omc_glu_mul": (_I, [_P, _L, _I, _I, _I, _P, _I, _L, _P]),
-    "omc_causal_conv_silu": (_I, [_P, _L, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _F, _I, _F, _P]),
+    "omc_glu_mul": (_I, [_P, _I, _L, _I, _I, _I, _P, _I, _L, _P]),
+    "omc_causal_conv_silu": (_I, [_P, _L, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _F, _I, _F, _I, _P]),
     "omc_linear_state_scan": (_I, [_P, _L, _P, _L, _P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _L, _P, _P, _L, _P, _I, _P, _P, _I, _I, _I, _I, _P]),
+    "omc_map_rows": (_I, [_P, _L, _I, _I, _I, _P, _P, _I, _P]),
     "omc_gated_rms_rows": (_I, [_P, _L, _I, _I, _I, _P, _I, _F, _P, _L, _I, _P, _I, _L, _P]),
     "omc_qk_norm_kv_store": (_I, [_P, _L, _I, _P, _P, _L, _I, _P, _I, _P, _L, _I, _F, _I, _P, _P, _P, _I, _I, _P, _P, _L, _I, _P]),
     "omc_window_attn": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P, _P, _I, _F, _F, _P, _P, _I, _L, _P]),
@@ -355,30 +356,33 @@ def post_norm_residual(y1: torch.Tensor, w_post: torch.Tensor, eps: float, mult:
 def glu_mul(z: torch.Tensor, n: int, act: int, out: torch.Tensor):
     """out[:, c] = act(z[:, c]) * z[:, n + c]."""
     _need_cuda(z, out)
-    assert z.dtype == torch.float32 and z.stride(1) == 1 and out.stride(1) == 1 and z.shape[1] >= 2 * n
-    rc = load().omc_glu_mul(_ptr(z), z.stride(0), z.shape[0], n, act, _ptr(out), _dt(out), out.stride(0), _stream())
+    assert z.stride(1) == 1 and out.stride(1) == 1 and z.shape[1] >= 2 * n
+    rc = load().omc_glu_mul(_ptr(z), _dt(z), z.stride(0), z.shape[0], n, act, _ptr(out), _dt(out), out.stride(0), _stream())
     _check(rc, "omc_glu_mul")
     return out
 
 
 # ---- state mixers
 GATE_NONE, GATE_SILU, GATE_SIGMOID = 0, 1, 2
-DECAY_CONST, DECAY_HEAD, DECAY_CHANNEL = 0, 1, 2
+DECAY_CONST, DECAY_HEAD, DECAY_CHANNEL, DECAY_GIVEN = 0, 1, 2, 3
+MAP_SILU, MAP_DECAY = 1, 2
 
 
 def causal_conv_silu(x: torch.Tensor, w: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor, state: Optional[torch.Tensor],
                      y: torch.Tensor, unit_channels: int = 0, unit_group: int = 0, unit_eps: float = 1e-6, scaled_channels: int = 0,
-                     unit_mult: float = 1.0):
-    """x fp32 [T, >= ch] (a column slice is fine), w [ch, taps], state fp32 [slots, taps - 1, ch] -> y fp32 [T, ch]."""
+                     unit_mult: float = 1.0, single_rows: bool = False):
+    """x fp32 [T, >= ch] (a column slice is fine), w [ch, taps], state fp32 [slots, taps - 1, ch] -> y fp32 [T, ch].
+    single_rows: every row is a request of its own (one launch instead of two)."""
     _need_cuda(x, w, pos, slot, state, y)
     ch, taps = w.shape
     assert x.dtype == torch.float32 and y.dtype == torch.float32 and x.stride(1) == 1 and y.stride(1) == 1 and w.is_contiguous()
     assert pos.dtype == torch.int32 and slot.dtype == torch.int32
     assert taps == 1 or (state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (taps - 1, ch))
     rc = load().omc_causal_conv_silu(_ptr(x), x.stride(0), x.shape[0], ch, _ptr(w), _dt(w), taps, _ptr(pos), _ptr(slot), _ptr(state),
-                                     _ptr(y), y.stride(0), unit_channels, unit_group, unit_eps, scaled_channels, unit_mult, _stream())
+                                     _ptr(y), y.stride(0), unit_channels, unit_group, unit_eps, scaled_channels, unit_mult,
+                                     1 if single_rows else 0, _stream())
     _check(rc, "omc_causal_conv_silu")
-    if taps > 1:
+    if taps > 1 and not single_rows:
         _core.add_launches(1)
     return y
 
@@ -386,15 +390,17 @@ def causal_conv_silu(x: torch.Tensor, w: torch.Tensor, pos: torch.Tensor, slot: 
 def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, out: torch.Tensor, row_begin: torch.Tensor,
                       portions: int, pos: torch.Tensor, slot: torch.Tensor, H: int, G: int, dim: int, vdim: int, *, silu_in: bool = False,
                       decay_const: Optional[torch.Tensor] = None, a: Optional[torch.Tensor] = None, A_log: Optional[torch.Tensor] = None,
-                      dt_bias: Optional[torch.Tensor] = None, channel_decay: bool = False, beta: Optional[torch.Tensor] = None):
-    """The recurrence of omc_linear_state_scan; q / k / v / a / beta are fp32 2-D tensors or column slices of one."""
+                      dt_bias: Optional[torch.Tensor] = None, channel_decay: bool = False, beta: Optional[torch.Tensor] = None,
+                      decay_given: bool = False):
+    """The recurrence of omc_linear_state_scan; q / k / v / a / beta are fp32 2-D tensors or column slices of one.
+    decay_given: `a` [T, H * dim] already holds the per-channel decays (map_rows(..., MAP_DECAY))."""
     _need_cuda(q, k, v, state, out, row_begin, pos, slot, decay_const, a, A_log, dt_bias, beta)
     for t in (q, k, v, out, a, beta):
         assert t is None or (t.dtype == torch.float32 and t.stride(1) == 1)
     for t in (decay_const, A_log, dt_bias):
         assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
     assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, dim, vdim) and row_begin.dtype == torch.int32
-    mode = DECAY_CONST if decay_const is not None else (DECAY_CHANNEL if channel_decay else DECAY_HEAD)
+    mode = DECAY_CONST if decay_const is not None else (DECAY_GIVEN if decay_given else (DECAY_CHANNEL if channel_decay else DECAY_HEAD))
     rc = load().omc_linear_state_scan(_ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), 1 if silu_in else 0, mode,
                                       _ptr(decay_const), _ptr(a), a.stride(0) if a is not None else 0, _ptr(A_log), _ptr(dt_bias),
                                       _ptr(beta), beta.stride(0) if beta is not None else 0, _ptr(state), _ptr(out), out.stride(0),
@@ -473,3 +479,12 @@ def window_attn_mma(q: torch.Tensor, H: int, G: int, d: int, dv: int, pool: torc
                                     scale, softcap, _ptr(dist_bias), _ptr(out), _dt(out), out.stride(0), _stream())
     _check(rc, "omc_window_attn_mma")
     return out
+
+
+def map_rows(x: torch.Tensor, op: int, A_log: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, group: int = 1):
+    """In place over the fp32 rows x (a column slice is fine): MAP_SILU, or MAP_DECAY: exp(-exp(A_log[c // group]) softplus(x + bias[c]))."""
+    _need_cuda(x, A_log, bias)
+    assert x.dtype == torch.float32 and x.stride(1) == 1
+    rc = load().omc_map_rows(_ptr(x), x.stride(0), x.shape[0], x.shape[1], op, _ptr(A_log), _ptr(bias), group, _stream())
+    _check(rc, "omc_map_rows")
+    return x

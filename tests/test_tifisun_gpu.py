@@ -162,7 +162,7 @@ def test_causal_conv_alone_and_in_portions(taps, ch, group):
         xin = torch.cat([_dev(xin), torch.zeros(xin.shape[0], 5, device=DEV)], dim=1)          # a column slice of a wider buffer
         y = torch.empty(xin.shape[0], ch, device=DEV)
         seqlib.causal_conv_silu(xin[:, :ch], _dev(w), pos, slot, state, y, unit_channels=unit, unit_group=group, unit_eps=1e-6,
-                                scaled_channels=unit // 2, unit_mult=0.37)
+                                scaled_channels=unit // 2, unit_mult=0.37, single_rows=all(n == 1 for _, _, _, n in step))
         at = 0
         for _, b, p0, n in step:
             got[b][p0:p0 + n] = y[at:at + n].double().cpu()
@@ -248,6 +248,7 @@ def test_linear_bias_and_gated_halves():
         z = seqlib.linear(xd, wd, torch.empty(70, 38, device=DEV), bias=bd)
         want = xd.double().cpu() @ wd.double().cpu().T + bd.double().cpu()
         assert torch.allclose(z.double().cpu(), want, atol=tol, rtol=tol)
+        z = z.to(dt)                                        # the gated halves are read in either dtype
         out = seqlib.glu_mul(z, 19, seqlib.ACT_GELU_TANH, torch.empty(70, 19, device=DEV))
         zz = z.double().cpu()
         assert torch.allclose(out.double().cpu(), O.gelu_tanh(zz[:, :19]) * zz[:, 19:], atol=1e-5, rtol=1e-5)

@@ -73,6 +73,17 @@ def kernels(z, n_seq, L, B, ctx):
         nbytes = T * H * (2 * d + 2 * dv) * 4 + extra + 2 * n_seq * H * d * dv * 4
         out[f"state_scan_prefill_{name}"] = {"ms": ms, "tflops": flops / ms / 1e9, "frac_fp32_fma": flops / ms / 1e9 / FMA_TFLOPS,
                                              "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / hbm}
+    # the same with silu / the per-channel decays applied by one pass in front (what a step with long portions does)
+    ms_map = timed(lambda: seqlib.map_rows(a2, seqlib.MAP_DECAY, A_log, dt2, d))
+    a2.uniform_(0.9, 1.0)
+    ms = timed(lambda: seqlib.linear_state_scan(q, k, v, state, o, rb, n_seq, pos, slot, H, H, d, dv, a=a2, beta=beta, decay_given=True))
+    out["state_scan_prefill_channel_prepared"] = {"ms": ms, "ms_decay_pass": ms_map, "tflops": flops / ms / 1e9, "frac_fp32_fma": flops / ms / 1e9 / FMA_TFLOPS}
+    qkv3 = torch.randn(T, 2 * H * d + H * dv, device=dev)
+    ms_map = timed(lambda: seqlib.map_rows(qkv3, seqlib.MAP_SILU))
+    ms = timed(lambda: seqlib.linear_state_scan(q, k, v, state, o, rb, n_seq, pos, slot, H, H, d, dv, decay_const=consts))
+    out["state_scan_prefill_const_prepared"] = {"ms": ms, "ms_silu_pass": ms_map, "tflops": flops / ms / 1e9, "frac_fp32_fma": flops / ms / 1e9 / FMA_TFLOPS}
+    del qkv3
+    a2.normal_()
     # ---- recurrence, decode: B rows, each reads and writes its states
     posd = torch.full((B,), ctx, dtype=i32, device=dev)
     slotd = torch.arange(B, dtype=i32, device=dev)
@@ -92,7 +103,10 @@ def kernels(z, n_seq, L, B, ctx):
     ms = timed(lambda: seqlib.window_attn(qb, H, G, d, dv, pool, table, page, pos, slot, W, d ** -0.5, 30.0, bias, att), reps=5, warm=2)
     visible = n_seq * sum(min(p + 1, W) for p in range(L))
     flops = visible * H * 2.0 * (d + dv)
-    out["window_attn_prefill"] = {"ms": ms, "tflops": flops / ms / 1e9, "frac_tensor": flops / ms / 1e9 / tf}
+    out["window_attn_plain_prefill"] = {"ms": ms, "tflops": flops / ms / 1e9, "frac_tensor": flops / ms / 1e9 / tf}
+    items = seqlib.window_attn_items([(s_ * L, L, s_, 0) for s_ in range(n_seq)], H // G, dev)
+    ms = timed(lambda: seqlib.window_attn_mma(qb, H, G, d, dv, pool, table, page, items, pos, slot, W, d ** -0.5, 30.0, bias, att))
+    out["window_attn_prefill"] = {"ms": ms, "tflops": flops / ms / 1e9, "frac_tensor": flops / ms / 1e9 / tf, "ctas": int(items.shape[0]) * G}
     qkv = (torch.randn(T, (H + 2 * G) * 128, device=dev) * 0.3).to(bf)
     cu = torch.arange(0, T + 1, L, dtype=i32, device=dev)
     ms = timed(lambda: lib.attention(qkv[:, :H * 128], qkv[:, H * 128:(H + G) * 128], qkv[:, (H + G) * 128:], att, cu, L, H, G, True, 0.088))
@@ -105,7 +119,9 @@ def kernels(z, n_seq, L, B, ctx):
     table = (torch.arange(B * pages_per, dtype=i32, device=dev) + 1).view(B, pages_per).contiguous()
     ms = timed(lambda: seqlib.window_attn(qb[:B], H, G, d, dv, pool, table, page, posd, slotd, W, d ** -0.5, 30.0, bias, att[:B]))
     nbytes = B * min(ctx + 1, W) * G * (d + dv) * 2
-    out["window_attn_decode"] = {"batch": B, "ctx": ctx, "ms": ms, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / hbm}
+    out["window_attn_plain_decode"] = {"batch": B, "ctx": ctx, "ms": ms, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / hbm}
+    ms = timed(lambda: seqlib.window_attn_mma(qb[:B], H, G, d, dv, pool, table, page, None, posd, slotd, W, d ** -0.5, 30.0, bias, att[:B]))
+    out["window_attn_decode"] = {"batch": B, "ctx": ctx, "ms": ms, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / hbm, "ctas": B * G}
     kvp = (torch.randn(B * pages_per + 1, 2, G, page, 128, device=dev) * 0.3).to(bf)
     qkv = (torch.randn(B, (H + 2 * G) * 128, device=dev) * 0.3).to(bf)
     lens = torch.full((B,), ctx + 1, dtype=i32, device=dev)
