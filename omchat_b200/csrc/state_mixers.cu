@@ -10,7 +10,8 @@
 // The recurrence is evaluated token by token in every case - prompt portions and single decoded tokens run the same
 // instructions in the same order, which makes the result independent of how a prompt is cut. Its parallelism is over the
 // independent COLUMNS of S: column j of a head's state only ever meets v[:, j], so a CTA owns 32 columns of one head of one
-// portion, eight lanes share a column (each holds an eighth of its state elements in registers, as packed fp32 pairs) and finish the
+// portion; a thread holds an eighth of the state elements of TWO neighbouring columns as packed fp32 pairs (one fma.rn.f32x2 serves
+// both columns, and a key or query value read from shared memory is used twice), and the eight lanes of a column pair finish the
 // two dot products of a token with three shuffles each. Tokens are staged 16 at a time in shared memory by cp.async, one chunk ahead of the one being
 // computed (decays, sigmoid and silu applied in place on arrival), so the sequential loop touches registers and shared memory only.
 #include "seq_common.cuh"
@@ -22,53 +23,66 @@ __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-
 __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 
 // ---- causal convolution + silu (+ unit vectors) ---------------------------------------------------------------------------
-// One CTA per (row, block of channels; blocks are whole unit-vector groups). Tap j of `taps` multiplies the input
+// One CTA per (1 or 8 consecutive rows, block of channels; blocks are whole unit-vector groups). Tap j of `taps` multiplies the input
 // `taps - 1 - j` positions back: an earlier row of the same step when that row belongs to the same request, else the state ring
 // state[slot][position % (taps - 1)][channel], else (before position 0) zero. save_here: every row of the step is a request of
 // its own, so the row's input goes into its ring from this kernel, after the reads (no other CTA reads that ring).
+constexpr int kConvRows = 8;    // rows per CTA of a long step: neighbouring rows read each other's inputs, which then come from L1
+constexpr int kConvMaxTaps = 16;
+
 template <typename TW>
-__global__ void __launch_bounds__(256) causal_conv_silu_kernel(const float* __restrict__ x, long long ldx, int ch, int ch_block,
-                                                               const TW* __restrict__ w, int taps, const int32_t* __restrict__ pos,
-                                                               const int32_t* __restrict__ slot, float* __restrict__ state,
-                                                               float* __restrict__ y, long long ldy, int unit_channels,
-                                                               int unit_group, float unit_eps, int scaled_channels, float unit_mult,
-                                                               int save_here) {
-  extern __shared__ float row[];  // [ch_block]
-  const int t = blockIdx.x, c0 = blockIdx.y * ch_block, nc = min(ch_block, ch - c0);
-  const int p = pos[t], s = slot[t], R = taps - 1;
-  for (int cl = threadIdx.x; cl < nc; cl += blockDim.x) {
-    const int c = c0 + cl;
-    float acc = 0.f;
-    for (int j = 0; j < taps; ++j) {
-      const int back = R - j, sp = p - back;
-      if (sp < 0) continue;
-      float xv;
-      if (back == 0 || (t - back >= 0 && slot[t - back] == s)) xv = x[(long long)(t - back) * ldx + c];
-      else xv = state[((long long)s * R + sp % R) * ch + c];
-      acc = fmaf(ldf(w + (long long)c * taps + j), xv, acc);
-    }
-    row[cl] = silu_f(acc);
+__global__ void __launch_bounds__(256) causal_conv_silu_kernel(const float* __restrict__ x, long long ldx, int T, int ch, int ch_block,
+                                                               int rows_per_cta, const TW* __restrict__ w, int taps,
+                                                               const int32_t* __restrict__ pos, const int32_t* __restrict__ slot,
+                                                               float* __restrict__ state, float* __restrict__ y, long long ldy,
+                                                               int unit_channels, int unit_group, float unit_eps, int scaled_channels,
+                                                               float unit_mult, int save_here) {
+  extern __shared__ float tile[];  // [rows_per_cta][ch_block]
+  __shared__ const float* src[kConvRows][kConvMaxTaps];   // where tap j of row r reads: a row of x, a ring entry, or nothing
+  const int t0 = blockIdx.x * rows_per_cta, nr = min(rows_per_cta, T - t0);
+  const int c0 = blockIdx.y * ch_block, nc = min(ch_block, ch - c0);
+  const int R = taps - 1;
+  if (threadIdx.x < nr * taps) {
+    const int r = threadIdx.x / taps, j = threadIdx.x - r * taps;
+    const int t = t0 + r, p = pos[t], s = slot[t], back = R - j, sp = p - back;
+    const float* q = nullptr;
+    if (sp >= 0) q = (back == 0 || (t - back >= 0 && slot[t - back] == s)) ? x + (long long)(t - back) * ldx : state + ((long long)s * R + sp % R) * ch;
+    src[r][j] = q;
   }
   __syncthreads();
-  if (save_here && R > 0) {
-    float* dst = state + ((long long)s * R + p % R) * ch;
-    for (int cl = threadIdx.x; cl < nc; cl += blockDim.x) dst[c0 + cl] = x[(long long)t * ldx + c0 + cl];
+  for (int cl = threadIdx.x; cl < nc; cl += blockDim.x) {
+    const int c = c0 + cl;
+    for (int r = 0; r < nr; ++r) {
+      float acc = 0.f;
+#pragma unroll 4
+      for (int j = 0; j < taps; ++j) {
+        const float* q = src[r][j];
+        const float xv = q != nullptr ? q[c] : 0.f;
+        acc = fmaf(ldf(w + (long long)c * taps + j), xv, acc);
+      }
+      tile[r * ch_block + cl] = silu_f(acc);
+      // this thread is the only one that touches channel c of the ring: its write follows its reads
+      if (save_here && R > 0) state[((long long)slot[t0 + r] * R + pos[t0 + r] % R) * ch + c] = x[(long long)(t0 + r) * ldx + c];
+    }
   }
+  __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const int unit_here = max(0, min(nc, unit_channels - c0));      // unit-vector channels of this block (whole groups)
   const int groups = unit_group > 0 ? unit_here / unit_group : 0;
-  for (int g = warp; g < groups; g += nw) {
+  for (int rg = warp; rg < nr * groups; rg += nw) {
+    const int r = rg / groups, g = rg - r * groups;
+    float* row = tile + r * ch_block + g * unit_group;
     float ss = 0.f;
-    for (int c = lane; c < unit_group; c += 32) {
-      const float v = row[g * unit_group + c];
-      ss = fmaf(v, v, ss);
-    }
+    for (int c = lane; c < unit_group; c += 32) ss = fmaf(row[c], row[c], ss);
     ss = seq_warp_sum(ss);
     const float f = (1.f / sqrtf(ss + unit_eps)) * (c0 + g * unit_group < scaled_channels ? unit_mult : 1.f);
-    for (int c = lane; c < unit_group; c += 32) row[g * unit_group + c] *= f;
+    for (int c = lane; c < unit_group; c += 32) row[c] *= f;
   }
   __syncthreads();
-  for (int cl = threadIdx.x; cl < nc; cl += blockDim.x) y[(long long)t * ldy + c0 + cl] = row[cl];
+  for (int e = threadIdx.x; e < nr * nc; e += blockDim.x) {
+    const int r = e / nc, cl = e - r * nc;
+    y[(long long)(t0 + r) * ldy + c0 + cl] = tile[r * ch_block + cl];
+  }
 }
 
 // The last taps - 1 inputs of every request of the step go into its ring (rows that are followed by taps - 1 more rows of the
@@ -135,15 +149,8 @@ __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
-__device__ __forceinline__ float sum2(f32x2 a, f32x2 b) {
-  float a0, a1, b0, b1;
-  unpack2(a, a0, a1);
-  unpack2(b, b0, b1);
-  return (a0 + a1) + (b0 + b1);
-}
-
 // Shared-memory place of key channel i: lane l = i / DPT owns DPT consecutive channels (read as float4), and a gap of four floats
-// between the lanes' blocks moves them to different banks (strides of 12, 20 and 36 floats spread eight float4 reads over all 32).
+// between the lanes' blocks moves them to different banks (the eight float4 reads of a quarter warp, at strides of 12, 20 or 36 floats, fall on different banks).
 template <int DPT>
 __device__ __forceinline__ int scan_place(int i) { return (i / DPT) * (DPT + 4) + (i % DPT); }
 
@@ -151,7 +158,7 @@ __device__ __forceinline__ int scan_place(int i) { return (i / DPT) * (DPT + 4) 
 // after arrival one pass turns them in place into what the recurrence uses (silu, decays, sigmoid). VEC: 16-byte copies
 // (every row starts on a 16-byte boundary and the widths are multiples of four), else 4-byte copies.
 template <int DPT, bool VEC>
-__global__ void __launch_bounds__(kScanCols * kScanLanes) linear_state_scan_kernel(ScanArgs a) {
+__global__ void __launch_bounds__(kScanCols / 2 * kScanLanes) linear_state_scan_kernel(ScanArgs a) {
   extern __shared__ __align__(16) float sm[];
   constexpr int PITCH = kScanLanes * (DPT + 4);
   const int dim = a.dim;
@@ -161,17 +168,18 @@ __global__ void __launch_bounds__(kScanCols * kScanLanes) linear_state_scan_kern
   const int col0 = blockIdx.x * kScanCols;
   const int r0 = a.row_begin[blockIdx.z], r1 = a.row_begin[blockIdx.z + 1];
   if (r1 <= r0) return;
-  const int tid = threadIdx.x, lane = tid & (kScanLanes - 1), col = col0 + (tid / kScanLanes);
-  const bool col_ok = col < a.vdim;
+  // thread = (lane over the key channels, PAIR of neighbouring columns): a packed register holds one key channel of both columns
+  const int tid = threadIdx.x, lane = tid & (kScanLanes - 1), cp = tid / kScanLanes, col = col0 + 2 * cp;
+  const bool ok0 = col < a.vdim, ok1 = col + 1 < a.vdim;
   for (int e = tid; e < 2 * stage_floats; e += blockDim.x) sm[e] = 0.f;   // the pads stay zero: they meet zero state only
   float* S = a.state + (((long long)a.slot[r0] * a.H + h) * dim) * a.vdim;
-  f32x2 st[DPT / 2];   // this thread's DPT state elements of its column, as pairs of neighbouring key channels
+  f32x2 st[DPT];   // state elements (lane * DPT + r, col) and (lane * DPT + r, col + 1)
   const bool fresh = a.pos[r0] == 0;
 #pragma unroll
-  for (int r = 0; r < DPT; r += 2) {
+  for (int r = 0; r < DPT; ++r) {
     const int i = lane * DPT + r;
-    const bool ld = !fresh && col_ok;
-    st[r / 2] = pack2((ld && i < dim) ? S[(long long)i * a.vdim + col] : 0.f, (ld && i + 1 < dim) ? S[(long long)(i + 1) * a.vdim + col] : 0.f);
+    const bool ld = !fresh && i < dim;
+    st[r] = pack2((ld && ok0) ? S[(long long)i * a.vdim + col] : 0.f, (ld && ok1) ? S[(long long)i * a.vdim + col + 1] : 0.f);
   }
   const float A = (a.decay_mode == 1 || a.decay_mode == 2) ? expf(a.A_log[h]) : 0.f;
   const float gconst = a.decay_mode == 0 ? a.decay_const[h] : 1.f;
@@ -252,65 +260,74 @@ __global__ void __launch_bounds__(kScanCols * kScanLanes) linear_state_scan_kern
     for (int tt = 0; tt < n; ++tt) {
       const float* kr = sk + tt * PITCH + lane * (DPT + 4);
       const float* qr = sq + tt * PITCH + lane * (DPT + 4);
-      f32x2 da = 0ull, db = 0ull;   // two packed accumulators = four partial sums
-      if (chan) {
-        const float* gr = sg + tt * PITCH + lane * (DPT + 4);
+      f32x2 da = 0ull, db = 0ull;   // (column, column + 1) partial dot products, two chains
+      f32x2 k2[DPT];                // the key, each channel doubled: used again by the update
+      const f32x2 gh = pack2(sg[chan ? 0 : tt], sg[chan ? 0 : tt]);
+      const float* gr = sg + tt * PITCH + lane * (DPT + 4);
 #pragma unroll
-        for (int r = 0; r < DPT; r += 4) {
-          const ulonglong2 kv = *reinterpret_cast<const ulonglong2*>(kr + r);
-          const ulonglong2 gv = *reinterpret_cast<const ulonglong2*>(gr + r);
-          st[r / 2] = mul2(st[r / 2], gv.x);
-          st[r / 2 + 1] = mul2(st[r / 2 + 1], gv.y);
-          da = fma2(st[r / 2], kv.x, da);
-          db = fma2(st[r / 2 + 1], kv.y, db);
+      for (int r = 0; r < DPT; r += 4) {
+        const float4 kv = *reinterpret_cast<const float4*>(kr + r);
+        k2[r] = pack2(kv.x, kv.x), k2[r + 1] = pack2(kv.y, kv.y), k2[r + 2] = pack2(kv.z, kv.z), k2[r + 3] = pack2(kv.w, kv.w);
+        if (chan) {
+          const float4 gv = *reinterpret_cast<const float4*>(gr + r);
+          st[r] = mul2(st[r], pack2(gv.x, gv.x)), st[r + 1] = mul2(st[r + 1], pack2(gv.y, gv.y));
+          st[r + 2] = mul2(st[r + 2], pack2(gv.z, gv.z)), st[r + 3] = mul2(st[r + 3], pack2(gv.w, gv.w));
+        } else {
+          st[r] = mul2(st[r], gh), st[r + 1] = mul2(st[r + 1], gh), st[r + 2] = mul2(st[r + 2], gh), st[r + 3] = mul2(st[r + 3], gh);
         }
-      } else {
-        const f32x2 g2 = pack2(sg[tt], sg[tt]);
-#pragma unroll
-        for (int r = 0; r < DPT; r += 4) {
-          const ulonglong2 kv = *reinterpret_cast<const ulonglong2*>(kr + r);
-          st[r / 2] = mul2(st[r / 2], g2);
-          st[r / 2 + 1] = mul2(st[r / 2 + 1], g2);
-          da = fma2(st[r / 2], kv.x, da);
-          db = fma2(st[r / 2 + 1], kv.y, db);
-        }
+        da = fma2(st[r], k2[r], da), db = fma2(st[r + 1], k2[r + 1], db);
+        da = fma2(st[r + 2], k2[r + 2], da), db = fma2(st[r + 3], k2[r + 3], db);
       }
-      float u = sv[tt * kScanCols + (tid / kScanLanes)];
+      const float2 vv = *reinterpret_cast<const float2*>(sv + tt * kScanCols + 2 * cp);
+      float u0 = vv.x, u1 = vv.y;
       if (a.beta != nullptr) {
-        float dot = sum2(da, db);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-        u = sb[tt] * (u - dot);
+        float a0, a1, b0, b1;
+        unpack2(da, a0, a1);
+        unpack2(db, b0, b1);
+        float dot0 = a0 + b0, dot1 = a1 + b1;
+#pragma unroll
+        for (int m = 1; m < kScanLanes; m <<= 1) {
+          dot0 += __shfl_xor_sync(0xffffffffu, dot0, m);
+          dot1 += __shfl_xor_sync(0xffffffffu, dot1, m);
+        }
+        u0 = sb[tt] * (u0 - dot0);
+        u1 = sb[tt] * (u1 - dot1);
       }
-      const f32x2 u2 = pack2(u, u);
+      const f32x2 u2 = pack2(u0, u1);
       f32x2 oa = 0ull, ob = 0ull;
 #pragma unroll
       for (int r = 0; r < DPT; r += 4) {
-        const ulonglong2 kv = *reinterpret_cast<const ulonglong2*>(kr + r);
-        const ulonglong2 qv = *reinterpret_cast<const ulonglong2*>(qr + r);
-        st[r / 2] = fma2(kv.x, u2, st[r / 2]);
-        st[r / 2 + 1] = fma2(kv.y, u2, st[r / 2 + 1]);
-        oa = fma2(st[r / 2], qv.x, oa);
-        ob = fma2(st[r / 2 + 1], qv.y, ob);
+        const float4 qv = *reinterpret_cast<const float4*>(qr + r);
+        st[r] = fma2(k2[r], u2, st[r]), st[r + 1] = fma2(k2[r + 1], u2, st[r + 1]);
+        st[r + 2] = fma2(k2[r + 2], u2, st[r + 2]), st[r + 3] = fma2(k2[r + 3], u2, st[r + 3]);
+        oa = fma2(st[r], pack2(qv.x, qv.x), oa), ob = fma2(st[r + 1], pack2(qv.y, qv.y), ob);
+        oa = fma2(st[r + 2], pack2(qv.z, qv.z), oa), ob = fma2(st[r + 3], pack2(qv.w, qv.w), ob);
       }
-      float o = sum2(oa, ob);
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      o += __shfl_xor_sync(0xffffffffu, o, 4);
-      if (lane == 0 && col_ok) a.out[(long long)(c0 + tt) * a.ldo + h * a.vdim + col] = o;
+      float o0, o1, p0, p1;
+      unpack2(oa, o0, o1);
+      unpack2(ob, p0, p1);
+      o0 += p0;
+      o1 += p1;
+#pragma unroll
+      for (int m = 1; m < kScanLanes; m <<= 1) {
+        o0 += __shfl_xor_sync(0xffffffffu, o0, m);
+        o1 += __shfl_xor_sync(0xffffffffu, o1, m);
+      }
+      if (lane == 0) {
+        float* dst = a.out + (long long)(c0 + tt) * a.ldo + h * a.vdim + col;
+        if (ok0) dst[0] = o0;
+        if (ok1) dst[1] = o1;
+      }
     }
     __syncthreads();   // the next iteration's copies overwrite the stage that was just read
   }
-  if (col_ok) {
 #pragma unroll
-    for (int r = 0; r < DPT; r += 2) {
-      const int i = lane * DPT + r;
-      float lo, hi;
-      unpack2(st[r / 2], lo, hi);
-      if (i < dim) S[(long long)i * a.vdim + col] = lo;
-      if (i + 1 < dim) S[(long long)(i + 1) * a.vdim + col] = hi;
-    }
+  for (int r = 0; r < DPT; ++r) {
+    const int i = lane * DPT + r;
+    float lo, hi;
+    unpack2(st[r], lo, hi);
+    if (i < dim && ok0) S[(long long)i * a.vdim + col] = lo;
+    if (i < dim && ok1) S[(long long)i * a.vdim + col + 1] = hi;
   }
 }
 
@@ -362,7 +379,7 @@ extern "C" int omc_causal_conv_silu(const float* x, long long ldx, int T, int ch
                                     const int32_t* pos, const int32_t* slot, float* state, float* y, long long ldy,
                                     int unit_channels, int unit_group, float unit_eps, int scaled_channels, float unit_mult,
                                     int single_rows, void* stream) {
-  if (x == nullptr || w == nullptr || pos == nullptr || slot == nullptr || y == nullptr || T < 0 || ch <= 0 || taps < 1 ||
+  if (x == nullptr || w == nullptr || pos == nullptr || slot == nullptr || y == nullptr || T < 0 || ch <= 0 || taps < 1 || taps > kConvMaxTaps ||
       (taps > 1 && state == nullptr) || unit_channels < 0 || unit_channels > ch || (unit_channels > 0 && (unit_group <= 0 || unit_channels % unit_group)) ||
       (unit_channels > 0 && scaled_channels % unit_group))
     return set_error(OMC_ERR_ARG, "omc_causal_conv_silu: bad argument");
@@ -371,14 +388,15 @@ extern "C" int omc_causal_conv_silu(const float* x, long long ldx, int T, int ch
   int ch_block = 512;
   if (unit_channels > 0) ch_block = unit_group >= 512 ? unit_group : (512 / unit_group) * unit_group;
   if (ch_block > ch) ch_block = ch;
-  if ((size_t)ch_block * sizeof(float) > 200 * 1024) return set_error(OMC_ERR_SHAPE, "omc_causal_conv_silu: unit-vector group too wide for shared memory");
+  if ((size_t)ch_block * kConvRows * sizeof(float) > 200 * 1024) return set_error(OMC_ERR_SHAPE, "omc_causal_conv_silu: unit-vector group too wide for shared memory");
   const int blocks = (ch + ch_block - 1) / ch_block;
   if (blocks > 65535) return set_error(OMC_ERR_SHAPE, "omc_causal_conv_silu: too many channel blocks");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const size_t smem = (size_t)ch_block * sizeof(float);
+  const int rows_per_cta = T >= 256 ? kConvRows : 1;   // short steps (decode) keep one CTA per row: there are few rows to share anything
+  const size_t smem = (size_t)ch_block * rows_per_cta * sizeof(float);
   OMC_DT_SWITCH(w_dt, TW, {
     if (smem > 48 * 1024) cudaFuncSetAttribute(causal_conv_silu_kernel<TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    causal_conv_silu_kernel<TW><<<dim3(T, blocks), 256, smem, st>>>(x, ldx, ch, ch_block, static_cast<const TW*>(w), taps, pos, slot, state, y,
+    causal_conv_silu_kernel<TW><<<dim3((T + rows_per_cta - 1) / rows_per_cta, blocks), 256, smem, st>>>(x, ldx, T, ch, ch_block, rows_per_cta, static_cast<const TW*>(w), taps, pos, slot, state, y,
                                                                     ldy, unit_channels, unit_group, unit_eps, scaled_channels, unit_mult,
                                                                     single_rows ? 1 : 0);
   })
@@ -402,11 +420,11 @@ extern "C" int omc_linear_state_scan(const float* q, long long ldq, const float*
   ScanArgs s{q, k, v, ldq, ldk, ldv, silu_in, decay_mode, decay_const, a, lda, A_log, dt_bias, beta, ldb, state, out, ldo,
              row_begin, pos, slot, H, G, dim, vdim};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int dpt = dim <= 32 ? 4 : (dim <= 64 ? 8 : (dim <= 128 ? 16 : 32));   // state elements per thread: dim / 8 lanes, rounded up
+  const int dpt = dim <= 32 ? 4 : (dim <= 64 ? 8 : (dim <= 128 ? 16 : 32));   // key channels per thread: dim / 8 lanes, rounded up to a float4
   const size_t stage_floats = (size_t)kScanTok * kScanLanes * (dpt + 4) * (decay_mode >= 2 ? 3 : 2) + kScanTok * kScanCols + 2 * kScanTok;
   const size_t smem = 2 * stage_floats * sizeof(float);
   dim3 grid((vdim + kScanCols - 1) / kScanCols, H, portions);
-  const int threads = kScanCols * kScanLanes;
+  const int threads = kScanCols / 2 * kScanLanes;
   auto al16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   const bool vec = dim % 4 == 0 && vdim % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ldv % 4 == 0 && al16(q) && al16(k) && al16(v) &&
                    (decay_mode < 2 || (lda % 4 == 0 && al16(a)));

@@ -31,7 +31,7 @@ from tools.bench_voduzen import peaks, timed  # noqa: E402
 # width, layers, heads, key/value heads of the windowed attention (and query/key heads of the delta layers), head widths, window, ff, vocab
 SIZES = {
     "s": dict(C=2048, L=6, H=16, G=4, d=128, dv=128, conv=4, window=512, rank=64, ff=5632, V=32768),
-    "m": dict(C=4096, L=6, H=32, G=8, d=128, dv=128, conv=4, window=512, rank=128, ff=11008, V=65536),
+    "m": dict(C=4096, L=6, H=32, G=8, d=128, dv=128, conv=4, window=512, rank=128, ff=8192, V=65536),
 }
 FMA_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12   # nominal fp32 FMA peak of the part: what the recurrence runs on
 
