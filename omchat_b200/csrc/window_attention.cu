@@ -175,6 +175,7 @@ struct WinMmaArgs {
   long long ldo;
   int max_pages, page_size, H, G, d, dv, window;
   float scale, softcap;
+  int bias_in_smem;       // the bias columns of this key/value head's query heads are staged in shared memory ([window][H / G])
 };
 
 template <int NV, typename TO>  // NV: 8-column output tiles, dv <= 8 * NV
@@ -184,6 +185,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
   bf16_t* Qs = reinterpret_cast<bf16_t*>(wsm_raw);
   bf16_t* Ks = Qs + kWmRows * pq;          // [2][64][pq]
   bf16_t* Vs = Ks + 2 * kWmKeys * pq;      // [2][64][pv]
+  float* sbias = reinterpret_cast<float*>(Vs + 2 * kWmKeys * pv);   // [window][rep] when bias_in_smem
   int first_row, n_tok, slot, first_pos;
   if (a.items != nullptr) {
     const int32_t* it = a.items + blockIdx.x * 4;
@@ -202,6 +204,8 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
     if (row < n_rows) w_cp_async16(wsmem_u32(dst), a.q + (long long)(first_row + row / rep) * a.ldq + (kvh * rep + row % rep) * d + c * 8);
     else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
   }
+  if (a.bias_in_smem)   // a lookup per score from global memory would be a chain of L2 round trips
+    for (int e = tid; e < a.window * rep; e += blockDim.x) sbias[e] = a.bias[(long long)(e / rep) * a.H + kvh * rep + e % rep];
   const int row0 = warp * 16 + g, row1 = row0 + 8;
   const int p0 = row0 < n_rows ? first_pos + row0 / rep : -1, p1 = row1 < n_rows ? first_pos + row1 / rep : -1;   // -1: no such row
   const int h0 = kvh * rep + row0 % rep, h1 = kvh * rep + row1 % rep;
@@ -274,7 +278,8 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
           if (dist >= 0 && dist < a.window) {
             v = s[n][e] * a.scale;
             if (a.softcap > 0.f) v = a.softcap * tanh_approx(v * inv_cap);
-            if (a.bias != nullptr) v += __ldg(a.bias + (long long)dist * a.H + hh);
+            if (a.bias_in_smem) v += sbias[dist * rep + (hh - kvh * rep)];
+            else if (a.bias != nullptr) v += __ldg(a.bias + (long long)dist * a.H + hh);
             v *= kLog2e;
           }
           s[n][e] = v;
@@ -408,9 +413,14 @@ extern "C" int omc_window_attn_mma(const void* q, long long ldq, int T, int H, i
   if (n == 0) return OMC_OK;
   if (G > 65535) return set_error(OMC_ERR_SHAPE, "omc_window_attn_mma: more than 65535 key/value heads");
   WinMmaArgs a{static_cast<const bf16_t*>(q), ldq, static_cast<const bf16_t*>(pool), block_table, items, pos, slot, dist_bias, out, ldo,
-               max_pages, page_size, H, G, d, dv, window, scale, softcap};
+               max_pages, page_size, H, G, d, dv, window, scale, softcap, 0};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const size_t smem = sizeof(bf16_t) * ((size_t)kWmRows * (d + 8) + 2 * (size_t)kWmKeys * (d + 8) + 2 * (size_t)kWmKeys * (dv + 8));
+  size_t smem = sizeof(bf16_t) * ((size_t)kWmRows * (d + 8) + 2 * (size_t)kWmKeys * (d + 8) + 2 * (size_t)kWmKeys * (dv + 8));
+  const size_t bias_bytes = sizeof(float) * (size_t)window * (H / G);
+  if (dist_bias != nullptr && bias_bytes <= 64 * 1024) {
+    a.bias_in_smem = 1;
+    smem += bias_bytes;
+  }
   dim3 grid(n, G);
 #define OMC_WIN_LAUNCH(NV, TO)                                                                                      \
   do {                                                                                                              \
