@@ -212,19 +212,20 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
   const int32_t* bt = a.bt + (long long)slot * a.max_pages;
   const int k_begin = max(0, first_pos - a.window + 1), k_end = first_pos + n_tok;
   const int roww = a.G * (d + dv);
+  // two threads per key: one page lookup per thread and tile, then 16-byte copies at a constant stride
   auto stage = [&](int buf, int j0) {
-    bf16_t* kb = Ks + buf * kWmKeys * pq;
-    bf16_t* vb = Vs + buf * kWmKeys * pv;
-    for (int i = tid; i < kWmKeys * (qchunks + vchunks); i += blockDim.x) {
-      const int key = i / (qchunks + vchunks), c = i - key * (qchunks + vchunks);
-      const int j = j0 + key;
-      bf16_t* dst = c < qchunks ? kb + key * pq + c * 8 : vb + key * pv + (c - qchunks) * 8;
-      if (j < k_end) {
-        const bf16_t* row = a.pool + ((long long)bt[j / a.page_size] * a.page_size + j % a.page_size) * roww;
-        w_cp_async16(wsmem_u32(dst), c < qchunks ? row + kvh * d + c * 8 : row + a.G * d + kvh * dv + (c - qchunks) * 8);
-      } else {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-      }
+    const int key = tid >> 1, half = tid & 1, j = j0 + key;
+    bf16_t* kd = Ks + (buf * kWmKeys + key) * pq;
+    bf16_t* vd = Vs + (buf * kWmKeys + key) * pv;
+    if (j < k_end) {
+      const bf16_t* row = a.pool + ((long long)bt[j / a.page_size] * a.page_size + j % a.page_size) * roww;
+      const bf16_t* ks = row + kvh * d;
+      const bf16_t* vs = row + a.G * d + kvh * dv;
+      for (int c = half; c < qchunks; c += 2) w_cp_async16(wsmem_u32(kd + c * 8), ks + c * 8);
+      for (int c = half; c < vchunks; c += 2) w_cp_async16(wsmem_u32(vd + c * 8), vs + c * 8);
+    } else {
+      for (int c = half; c < qchunks; c += 2) *reinterpret_cast<uint4*>(kd + c * 8) = make_uint4(0, 0, 0, 0);
+      for (int c = half; c < vchunks; c += 2) *reinterpret_cast<uint4*>(vd + c * 8) = make_uint4(0, 0, 0, 0);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
