@@ -146,7 +146,7 @@ int omc_glu_mul(const void* z, int z_dt, long long ldz, int rows, int n, int act
 
 /* Causal convolution over time per channel, then silu, then optional unit vectors. Row t is position pos[t] of the request in
  * state slot slot[t]; rows of one request are consecutive and ascending. w [ch, taps] of w_dt: the last tap multiplies the row
- * itself (taps <= 16), tap j the input taps - 1 - j positions back - an earlier row of the step, else state[slot][position % (taps - 1)][ch]
+ * itself (taps <= 32), tap j the input taps - 1 - j positions back - an earlier row of the step, else state[slot][position % (taps - 1)][ch]
  * (fp32 ring of the last taps - 1 inputs, updated by this call), else zero before position 0. Of the outputs the first
  * unit_channels are divided, in groups of unit_group, by sqrt(sum of squares + unit_eps); the first scaled_channels of those are
  * then multiplied by unit_mult (scaled_channels a multiple of unit_group). x / y fp32 (y may not alias x). single_rows != 0: the

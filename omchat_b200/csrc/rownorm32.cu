@@ -116,18 +116,47 @@ __global__ void __launch_bounds__(256) post_norm_residual_kernel(const float* __
 }
 
 // out = act(gate) * up over the two halves of a stacked projection: z [rows, 2 * n] -> out [rows, n]; the arithmetic is fp32.
-template <typename TZ, typename TY>
+// Four neighbouring columns per thread (8- or 16-byte accesses) when the rows are laid out for it, else one.
+__device__ __forceinline__ void ld4(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+}
+__device__ __forceinline__ void ld4(const bf16_t* p, float (&v)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+  v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y;
+}
+__device__ __forceinline__ void st4(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void st4(bf16_t* p, const float (&v)[4]) {
+  uint2 t;
+  *reinterpret_cast<__nv_bfloat162*>(&t.x) = __floats2bfloat162_rn(v[0], v[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&t.y) = __floats2bfloat162_rn(v[2], v[3]);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+__device__ __forceinline__ float glu_act(float g, int act) {
+  if (act == OMC_ACT_GELU_TANH) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  if (act == OMC_ACT_RELU2) return fmaxf(g, 0.f) * fmaxf(g, 0.f);
+  return g;
+}
+
+template <typename TZ, typename TY, int VEC>
 __global__ void __launch_bounds__(256) glu_mul_kernel(const TZ* __restrict__ z, long long ldz, int n, int act, TY* __restrict__ y,
                                                       long long ldy, long long total) {
-  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // one thread per VEC columns
   if (e >= total) return;
-  const long long t = e / n;
-  const int c = (int)(e - t * n);
-  float g = ldf(z + t * ldz + c);
-  const float u = ldf(z + t * ldz + n + c);
-  if (act == OMC_ACT_GELU_TANH) g = 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
-  else if (act == OMC_ACT_RELU2) g = fmaxf(g, 0.f) * fmaxf(g, 0.f);
-  stf(y + t * ldy + c, g * u);
+  const int per_row = n / VEC;
+  const long long t = e / per_row;
+  const int c = (int)(e - t * per_row) * VEC;
+  if (VEC == 4) {
+    float g[4], u[4];
+    ld4(z + t * ldz + c, g);
+    ld4(z + t * ldz + n + c, u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) g[i] = glu_act(g[i], act) * u[i];
+    st4(y + t * ldy + c, g);
+  } else {
+    stf(y + t * ldy + c, glu_act(ldf(z + t * ldz + c), act) * ldf(z + t * ldz + n + c));
+  }
 }
 
 }  // namespace omc
@@ -191,8 +220,10 @@ extern "C" int omc_glu_mul(const void* z, int z_dt, long long ldz, int rows, int
   if (rows == 0) return OMC_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long total = (long long)rows * n;
+  const bool vec = n % 4 == 0 && ldz % 4 == 0 && ldy % 4 == 0 && reinterpret_cast<uintptr_t>(z) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0;
   OMC_DT_SWITCH(z_dt, TZ, OMC_DT_SWITCH(y_dt, TY, {
-    glu_mul_kernel<TZ, TY><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(static_cast<const TZ*>(z), ldz, n, act, static_cast<TY*>(y), ldy, total);
+    if (vec) glu_mul_kernel<TZ, TY, 4><<<(unsigned)((total / 4 + 255) / 256), 256, 0, st>>>(static_cast<const TZ*>(z), ldz, n, act, static_cast<TY*>(y), ldy, total / 4);
+    else glu_mul_kernel<TZ, TY, 1><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(static_cast<const TZ*>(z), ldz, n, act, static_cast<TY*>(y), ldy, total);
   }))
   return check_launch("omc_glu_mul");
 }

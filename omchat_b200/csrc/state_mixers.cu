@@ -28,7 +28,7 @@ __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + lo
 // state[slot][position % (taps - 1)][channel], else (before position 0) zero. save_here: every row of the step is a request of
 // its own, so the row's input goes into its ring from this kernel, after the reads (no other CTA reads that ring).
 constexpr int kConvRows = 8;    // rows per CTA of a long step: neighbouring rows read each other's inputs, which then come from L1
-constexpr int kConvMaxTaps = 16;
+constexpr int kConvMaxTaps = 32;
 
 template <typename TW>
 __global__ void __launch_bounds__(256) causal_conv_silu_kernel(const float* __restrict__ x, long long ldx, int T, int ch, int ch_block,

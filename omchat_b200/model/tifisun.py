@@ -178,7 +178,7 @@ def weights_from_state_dict(sd: Dict[str, torch.Tensor], cfg: TifisunConfig, dev
     return TifisunW(embed=g("embed"), final_norm=g("final.norm"), head=g("head"), layers=layers)
 
 
-def random_state_dict(cfg: TifisunConfig, seed: int = 0, decay_rank: int = 16, gate_rank: int = 16, bias_rows: int = 16) -> Dict[str, torch.Tensor]:
+def random_state_dict(cfg: TifisunConfig, seed: int = 0, decay_rank: int = 16, gate_rank: int = 16, bias_rows: int = 32) -> Dict[str, torch.Tensor]:
     """Random bf16 weights under the checkpoint names (benchmarks, tests)."""
     gen = torch.Generator().manual_seed(seed)
 

@@ -72,7 +72,7 @@ def config_c(page=16):
 
 def config_d(page=16):
     """Attention shapes the tensor-core kernel takes (bf16): grouped heads, a window over several key tiles, two such layers."""
-    return {"architecture": "Tifisun", "vocab": 110, "width": 64, "embedding": {"scale": 3.0}, "residual_mult": 0.7, "norm": {"eps": 1e-5},
+    return {"architecture": "Tifisun", "vocab": 110, "width": 64, "embedding": {"scale": 3.5}, "residual_mult": 0.75, "norm": {"eps": 1e-5},
             "kv_page_size": page, "layers": [
                 parallel(4, 2, 32, 16, 75, 2, 16, 32, [0.9, 0.99], softcap=20.0, bias_max=80),
                 delta(2, 2, 32, 32, 4),
@@ -252,6 +252,13 @@ def test_linear_bias_and_gated_halves():
         out = seqlib.glu_mul(z, 19, seqlib.ACT_GELU_TANH, torch.empty(70, 19, device=DEV))
         zz = z.double().cpu()
         assert torch.allclose(out.double().cpu(), O.gelu_tanh(zz[:, :19]) * zz[:, 19:], atol=1e-5, rtol=1e-5)
+    # four columns per thread when the halves are a multiple of four wide
+    for dt in (torch.float32, torch.bfloat16):
+        z = _dev(torch.randn(33, 2 * 24, generator=g), dt)
+        for odt in (torch.float32, torch.bfloat16):
+            out = seqlib.glu_mul(z, 24, seqlib.ACT_GELU_TANH, torch.empty(33, 24, device=DEV, dtype=odt))
+            zz = z.double().cpu()
+            assert torch.allclose(out.double().cpu(), O.gelu_tanh(zz[:, :24]) * zz[:, 24:], atol=1e-5 if odt == torch.float32 else 2e-2, rtol=1e-2)
     # the aligned bf16 shape takes the tensor-core kernel of the library: same check there
     x, w, b = torch.randn(130, 64, generator=g), torch.randn(136, 64, generator=g), torch.randn(136, generator=g)
     xd, wd, bd = _dev(x, torch.bfloat16), _dev(w, torch.bfloat16), _dev(b, torch.bfloat16)
@@ -485,6 +492,22 @@ def test_mixed_batches_reused_pages_and_slots(dtype):
     for k in toks:
         assert len(got[k]) == lens[k]
         assert rel_err(torch.stack(got[k]), want[k]) < TOL[dtype], k
+
+
+def test_wide_layers_take_the_tensor_core_gemms():
+    """Width 1024: the stacked projections, gate | up (with bias) and down go through the tcgen05 GEMM in prompt portions and through
+    the skinny GEMM in decode rows; both against the oracle, and against each other."""
+    cd = {"architecture": "Tifisun", "vocab": 520, "width": 1024, "embedding": {"scale": 2.0}, "residual_mult": 0.6, "norm": {"eps": 1e-5},
+          "kv_page_size": 64, "layers": [delta(8, 4, 64, 128, 4, ff=1024), parallel(8, 2, 64, 64, 48, 4, 64, 128, [0.9, 0.95, 0.99, 0.999], ff=1024),
+                                         delta(8, 8, 64, 64, 3, channel=True, ff=1024)]}
+    model, sd = build(cd, torch.bfloat16, seed=17)
+    toks = tokens_for(cd, 80, 18)
+    want = oracle_logits(cd, sd, toks)
+    whole, _ = run_schedule(model, [([("w", toks, list(range(80)))], ["w"])], 128)
+    assert rel_err(torch.stack(whole["w"]), want) < TOL[torch.bfloat16]
+    steps = [([("p", toks[:70], [69])], [])] + [([("p", [t], [0])], []) for t in toks[70:]]
+    parts, _ = run_schedule(model, steps, 128)
+    assert rel_err(torch.stack(parts["p"]), want[69:]) < TOL[torch.bfloat16]
 
 
 def test_more_requests_than_slots_is_refused_and_pool_exhaustion_is_reported():

@@ -41,10 +41,10 @@ def config_dict(z):
     dl = {"conv": z["conv"], "dim": z["d"], "heads": z["H"], "kv_heads": z["H"] // 2, "vdim": z["dv"]}
     cd = {"conv": z["conv"], "dim": z["d"], "heads": z["H"], "kv_heads": z["H"], "vdim": z["dv"]}
     par = {"left": {"bias_max": z["window"], "dim": z["d"], "heads": z["H"], "kv_heads": z["G"], "mask": {"size": z["window"]},
-                    "scale": z["d"] ** -0.5, "softcap": 30.0, "vdim": z["dv"]},
+                    "scale": z["d"] ** -0.5, "softcap": 50.0, "vdim": z["dv"]},
            "right": {"decay": [1.0 - 2.0 ** (-3 - 6 * i / z["H"]) for i in range(z["H"])], "dim": z["d"], "heads": z["H"], "vdim": z["dv"]}}
     kinds = [("delta", dl), ("parallel", par), ("channel_delta", cd)]
-    return {"architecture": "Tifisun", "vocab": z["V"], "width": z["C"], "embedding": {"scale": 1.0}, "residual_mult": 0.7,
+    return {"architecture": "Tifisun", "vocab": z["V"], "width": z["C"], "embedding": {"scale": 1.0}, "residual_mult": 0.5,
             "norm": {"eps": 1e-5}, "layers": [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": mlp} for i in range(z["L"])]}
 
 
@@ -100,12 +100,12 @@ def kernels(z, n_seq, L, B, ctx):
     qb = (torch.randn(T, H * d, device=dev) * 0.3).to(bf)
     att = torch.empty(T, H * dv, device=dev, dtype=bf)
     bias = torch.randn(W, H, device=dev)
-    ms = timed(lambda: seqlib.window_attn(qb, H, G, d, dv, pool, table, page, pos, slot, W, d ** -0.5, 30.0, bias, att), reps=5, warm=2)
+    ms = timed(lambda: seqlib.window_attn(qb, H, G, d, dv, pool, table, page, pos, slot, W, d ** -0.5, 50.0, bias, att), reps=5, warm=2)
     visible = n_seq * sum(min(p + 1, W) for p in range(L))
     flops = visible * H * 2.0 * (d + dv)
     out["window_attn_plain_prefill"] = {"ms": ms, "tflops": flops / ms / 1e9, "frac_tensor": flops / ms / 1e9 / tf}
     items = seqlib.window_attn_items([(s_ * L, L, s_, 0) for s_ in range(n_seq)], H // G, dev)
-    ms = timed(lambda: seqlib.window_attn_mma(qb, H, G, d, dv, pool, table, page, items, pos, slot, W, d ** -0.5, 30.0, bias, att))
+    ms = timed(lambda: seqlib.window_attn_mma(qb, H, G, d, dv, pool, table, page, items, pos, slot, W, d ** -0.5, 50.0, bias, att))
     out["window_attn_prefill"] = {"ms": ms, "tflops": flops / ms / 1e9, "frac_tensor": flops / ms / 1e9 / tf, "ctas": int(items.shape[0]) * G}
     qkv = (torch.randn(T, (H + 2 * G) * 128, device=dev) * 0.3).to(bf)
     cu = torch.arange(0, T + 1, L, dtype=i32, device=dev)
@@ -117,10 +117,10 @@ def kernels(z, n_seq, L, B, ctx):
     pages_per = -(-(ctx + 1) // page)
     pool = (torch.randn(B * pages_per + 1, page, G * (d + dv), device=dev) * 0.3).to(bf)
     table = (torch.arange(B * pages_per, dtype=i32, device=dev) + 1).view(B, pages_per).contiguous()
-    ms = timed(lambda: seqlib.window_attn(qb[:B], H, G, d, dv, pool, table, page, posd, slotd, W, d ** -0.5, 30.0, bias, att[:B]))
+    ms = timed(lambda: seqlib.window_attn(qb[:B], H, G, d, dv, pool, table, page, posd, slotd, W, d ** -0.5, 50.0, bias, att[:B]))
     nbytes = B * min(ctx + 1, W) * G * (d + dv) * 2
     out["window_attn_plain_decode"] = {"batch": B, "ctx": ctx, "ms": ms, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / hbm}
-    ms = timed(lambda: seqlib.window_attn_mma(qb[:B], H, G, d, dv, pool, table, page, None, posd, slotd, W, d ** -0.5, 30.0, bias, att[:B]))
+    ms = timed(lambda: seqlib.window_attn_mma(qb[:B], H, G, d, dv, pool, table, page, None, posd, slotd, W, d ** -0.5, 50.0, bias, att[:B]))
     out["window_attn_decode"] = {"batch": B, "ctx": ctx, "ms": ms, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / hbm, "ctas": B * G}
     kvp = (torch.randn(B * pages_per + 1, 2, G, page, 128, device=dev) * 0.3).to(bf)
     qkv = (torch.randn(B, (H + 2 * G) * 128, device=dev) * 0.3).to(bf)
@@ -195,21 +195,24 @@ def qwen2_dense(z, batches, ctx, steps, prefill):
     out.append({"phase": "prefill", "tokens": T, "ms": ms, "tokens_per_sec": T / ms * 1e3})
     del cache, emb
     for B in batches:
-        cache = dec.new_cache(B, ctx + 2 * steps + 16)
-        cache.host_lens = [ctx] * B
-        cache.ctx_lens.fill_(ctx)
-        cache.pool.normal_(0, 0.5)
-        toks = torch.randint(0, cfg.vocab_size, (B,), device="cuda:0")
-        dec.generate_greedy(toks, cache, 8)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        dec.generate_greedy(toks, cache, steps)
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / steps
-        out.append({"phase": "decode", "batch": B, "ctx": ctx, "ms_per_step": ms, "tokens_per_sec": B / ms * 1e3})
-        del cache
+        try:
+            cache = dec.new_cache(B, ctx + 2 * steps + 16)
+            cache.host_lens = [ctx] * B
+            cache.ctx_lens.fill_(ctx)
+            cache.pool.normal_(0, 0.5)
+            toks = torch.randint(0, cfg.vocab_size, (B,), device="cuda:0")
+            dec.generate_greedy(toks, cache, 8)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            dec.generate_greedy(toks, cache, steps)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / steps
+            out.append({"phase": "decode", "batch": B, "ctx": ctx, "ms_per_step": ms, "tokens_per_sec": B / ms * 1e3})
+            del cache
+        except Exception as e:  # noqa: BLE001  (a decode path of that model that does not take these sizes)
+            out.append({"phase": "decode", "batch": B, "error": f"{type(e).__name__}: {e}"[:200]})
     dec.release()
     return out
 
