@@ -316,6 +316,8 @@ class WindowAttentionSpec:
         half = rows // 2
         if n < half:
             return n
+        if half < 1 or far <= half:      # no logarithmic range to spread over: everything further shares the last row
+            return rows - 1
         return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
 
 
