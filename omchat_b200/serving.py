@@ -13,7 +13,8 @@ Every request produces exactly the tokens a stand-alone greedy generate() of the
 near-ties: the split of the keys over CTAs depends on the batch size) - tests/test_serving_gpu.py checks that against the
 oracle.
 
-`StepScheduler` is the token-level loop for models that expose `step()` over (slot, position)-addressed rows (model/voduzen.py):
+`StepScheduler` is the token-level loop for models that expose `step()` over (slot, position)-addressed rows (model/voduzen.py,
+model/tifisun.py):
 every step is ONE packed batch in which portions of prompts run beside the single decode rows of other requests; pages are
 taken one by one as a request grows and go back to the free list when it ends, slots likewise.
 """
@@ -199,7 +200,8 @@ class _GenRequest:
 
 
 class StepScheduler:
-    """Token-level continuous batching over a PagedLatentCache.
+    """Token-level continuous batching over a PagedLatentCache (or a PagedStateCache: the slot a request holds is also where its
+    recurrent states live; the model's kernels start from zero at position 0, so nothing is cleared when a slot changes hands).
 
     model: exposes `decoder.new_cache(n_pages, n_slots)`, `config.kv_page_size` and
     `step(tokens, pos, slot, cache, want_rows) -> fp32 logits`. max_tokens: the most tokens live requests hold at any time,
